@@ -50,6 +50,17 @@ typedef void* umbs_stream_t; /* cudaStream_t */
 /* Gated activation of a gate|up pair of products (the `dual` argument of umbs_gemm; 0 = plain product). */
 #define UMBS_ACT_CLAMPED_GLU 1       /* g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit) */
 #define UMBS_ACT_GELU_TANH 2         /* gelu_tanh(g) u */
+#define UMBS_ACT_SILU 3              /* g sigmoid(g) u */
+
+/* Norm of the pre-norm layer form. */
+#define UMBS_NORM_RMS 0              /* x / sqrt(mean(x^2) + eps) * (offset + w) */
+#define UMBS_NORM_LAYER 1            /* (x - mean) / sqrt(mean((x - mean)^2) + eps) * (offset + w) + b */
+
+/* How a router turns its logits into experts and weights. */
+#define UMBS_ROUTE_SOFTMAX_TOP 0     /* the `top` largest logits, softmax over them */
+#define UMBS_ROUTE_SIGMOID_GROUPS 1  /* scores sigmoid(z); the experts form `groups` equal groups of neighbours, a group
+                                      * scores the sum of its two largest scores, only experts of the `keep` best groups are
+                                      * eligible; the `top` largest eligible scores, divided by their sum (+ 1e-20) */
 
 /* How attention turns scores into weights. */
 #define UMBS_ATTN_SOFTMAX 0          /* p = exp(s) / sum exp(s) */
@@ -87,6 +98,11 @@ typedef struct {
     const void* ws_gu;         /* [2 shared_ff, width] */
     const void* ws_down;       /* [width, shared_ff] */
     int act;                   /* UMBS_ACT_* of both parts */
+    int route_mode;            /* UMBS_ROUTE_* */
+    int groups, keep;          /* UMBS_ROUTE_SIGMOID_GROUPS: number of expert groups and how many stay eligible */
+    const float* bias_gu;      /* fp32 [2 shared_ff] or NULL: biases of the shared (dense) gate rows, then of its up rows */
+    const float* bias_down;    /* fp32 [width] or NULL: bias of the shared (dense) down projection */
+    const float* w_shared_gate;/* fp32 [width] or NULL: the shared expert's output is multiplied by sigmoid(w . h), a number per token */
 } umbs_mlp_t;
 
 typedef struct {
@@ -145,6 +161,21 @@ typedef struct {
     float* conv_state;         /* fp32 [2, slots, taps - 1, heads dim + kv_heads dim]: the last projected q | k rows
                                 * (double-buffered by the sequence's parity, as the shift state) */
     float* mlstm_state;        /* fp32 [slots, heads, dim (vdim + 1) + 1]: S with n as column vdim, then m */
+    /* pre-norm form, further options */
+    int norm_kind;             /* UMBS_NORM_* of norm_w / norm2_w */
+    const float* norm_b;       /* fp32 [width]: bias of a layer norm */
+    const float* norm2_b;
+    const float* out_scale;    /* fp32 [width] or NULL: the mixer's output is multiplied by it element by element (layer scale) */
+    const float* out_scale2;   /* the same for the feed-forward's output */
+    float residual_mult;       /* x += residual_mult * block output (0 reads as 1) */
+    /* latent attention in the pre-norm form (uses heads, dim, vdim, kv_rank, window (0: every earlier token), ring,
+     * ring_len, scale, kv_norm, w_ukT, w_uv, w_ukv, rot_dims, inv_freq, rot_mag, attn_mode, gate_kind (0 or 2) from above).
+     * q_rank == 0: queries come straight from the layer input.  w_in rows: q (heads (dim + rope_dim)) | latent (kv_rank) |
+     * shared rotated key part (rope_dim) | gate (heads vdim with gate_kind 2).  Every head's query is [dim | rope_dim]; its
+     * key is [W_uk latent | the shared part]; positions turn the first rot_dims dimensions of the rope_dim part.  A ring
+     * row holds [latent | rotated shared part], kv_rank + rope_dim numbers. */
+    int rope_dim;
+    const float* sink;         /* fp32 [heads] or NULL: with UMBS_ATTN_SOFTMAX_SINK the denominator also holds exp(sink[h]) (NULL: 1) */
 } umbs_layer_t;
 
 typedef struct {
@@ -157,6 +188,9 @@ typedef struct {
     const umbs_layer_t* layers;/* host array */
     float norm_offset;         /* added to the final norm's weight */
     float logit_softcap;       /* > 0: logits <- cap tanh(logits / cap) */
+    float embed_scale;         /* the embedding row is multiplied by it (0 reads as 1) */
+    int norm_kind;             /* UMBS_NORM_* of the final norm (pre-norm form) */
+    const float* final_norm_b; /* fp32 [width]: bias of a final layer norm */
 } umbs_model_t;
 
 const char* umbs_version(void);
@@ -180,6 +214,14 @@ int umbs_forward(const umbs_model_t* model, const umbs_batch_t* batch, float* lo
 int umbs_gemm(int dtype, const void* A, int64_t lda, int a_goff, const void* W, int64_t ldw, int64_t w_gstride, void* C,
               int64_t ldc, int c_goff, int c_f32, int M, int N, int K, int groups, const int32_t* grp_off,
               const int32_t* row_src, int dual, float limit, umbs_stream_t stream);
+
+/* umbs_gemm with an epilogue: bias (fp32 [N], with dual [2 N]: gate rows' then up rows'; the same for every group, or
+ * NULL) is added to the sums before the activation; out_gate (fp32, or NULL) multiplies the result by
+ * sigmoid(out_gate[row ld_gate + g gate_goff + n]).  dual: UMBS_ACT_*. */
+int umbs_gemm_ex(int dtype, const void* A, int64_t lda, int a_goff, const void* W, int64_t ldw, int64_t w_gstride, void* C,
+                 int64_t ldc, int c_goff, int c_f32, int M, int N, int K, int groups, const int32_t* grp_off,
+                 const int32_t* row_src, int dual, float limit, const float* bias, const float* out_gate, int64_t ld_gate,
+                 int gate_goff, umbs_stream_t stream);
 
 /* h = group_rms_norm(x) * w (groups equal consecutive parts, eps inside the root); hs = h + (h_prev - h) * shift_w
  * with h_prev the previous token's h (the slot's state for the first token of a step, zero at position 0).  Writes
@@ -225,6 +267,25 @@ int umbs_window_attention(int dtype, const void* q, int64_t ldq, const void* k, 
                           const umbs_batch_t* batch, int heads, int dim, int vdim, int window, float scale, void* out,
                           int64_t ldo, umbs_stream_t stream);
 
+/* The same over keys that carry a part all heads share: a key row (of c and of the ring) is [latent (kv_rank) | shared
+ * part (rope_dim)], a query row of q_abs [n_tokens, heads, kv_rank + rope_dim] likewise; the score is the dot product over
+ * all kv_rank + rope_dim numbers, the value is the latent.  window <= 0: every earlier token (the ring then holds the whole
+ * sequence).  mode: UMBS_ATTN_SOFTMAX or UMBS_ATTN_SOFTMAX_SINK, where the denominator also holds exp(sink[head]) (sink
+ * NULL: exp(0)).  out: `dtype` [n_tokens, heads, kv_rank].  kv_rank <= 512, kv_rank + rope_dim <= 640. */
+int umbs_latent_attention_ex(int dtype, const float* q_abs, const void* c, const void* ring, int ring_len,
+                             const umbs_batch_t* batch, int heads, int kv_rank, int rope_dim, int window, float scale, int mode,
+                             const float* sink, float* split_scratch, size_t split_bytes, void* out, umbs_stream_t stream);
+
+/* What stands between the in-projection of a latent-attention layer with direct queries and its attention kernel.
+ * proj: fp32 [n_tokens, ld] = [q (heads (dim + rope_dim)) | latent (kv_rank) | shared key part (rope_dim) | ...].
+ * c (`dtype` [n_tokens, kv_rank + rope_dim]) = [latent / rms(latent) * kv_norm | shared part turned by its position];
+ * q (`dtype` [n_tokens, heads, dim + rope_dim]) = every head's query with its last rope_dim numbers turned; q_rot (fp32, row
+ * stride ld_qrot per head, or NULL) gets each head's turned part again, in fp32.  The turn: pairs (i, i + rot_dims / 2) of
+ * the first rot_dims of the rope_dim numbers, angle = position inv_freq[i], cos and sin times rot_mag. */
+int umbs_latent_prep(int dtype, const float* proj, int64_t ld, const umbs_batch_t* batch, int heads, int dim, int rope_dim,
+                     int kv_rank, const float* kv_norm, float eps, int rot_dims, const float* inv_freq, float rot_mag, void* q,
+                     void* c, float* q_rot, int64_t ld_qrot, umbs_stream_t stream);
+
 /* Stores this step's latents into the slots' rings (position p at row p mod ring_len). */
 int umbs_ring_append(int dtype, const void* c, void* ring, int ring_len, const umbs_batch_t* batch, int kv_rank,
                      umbs_stream_t stream);
@@ -235,6 +296,15 @@ int umbs_ring_append(int dtype, const void* c, void* ring, int ring_len, const u
 int umbs_moe_route(int dtype, const void* h, int n, int width, const float* w_router, int experts, int top,
                    float* sel_w, int32_t* grp_off, int32_t* pair_tok, int32_t* pair_pos, int32_t* scratch,
                    umbs_stream_t stream);
+
+/* umbs_moe_route with the rule as an argument (mode: UMBS_ROUTE_*; groups, keep: see UMBS_ROUTE_SIGMOID_GROUPS; at most 64
+ * groups).  Ties go to the lower index. */
+int umbs_moe_route_ex(int dtype, const void* h, int n, int width, const float* w_router, int experts, int top, int mode,
+                      int groups, int keep, float* sel_w, int32_t* grp_off, int32_t* pair_tok, int32_t* pair_pos,
+                      int32_t* scratch, umbs_stream_t stream);
+
+/* g[t] = sigmoid(w . h[t]) in fp32; h: `dtype` [n, width], w: fp32 [width]. */
+int umbs_token_gate(int dtype, const void* h, int n, int width, const float* w, float* g, umbs_stream_t stream);
 
 /* X_next = x + (mix + (sum_k sel_w[t,k] pair_out[pair_pos[t,k]] + shared)); stores it at stack[layer + 1] and writes
  * x_out = sum_j depth_w[j] stack[j] (j <= layer + 1), or X_next itself when depth_w is NULL.  All fp32 [n, width];
@@ -250,6 +320,26 @@ int umbs_depth_mix(const float* x, const float* mix, const float* pair_out, cons
  * rows != NULL: y[r] is the norm of x[rows[r]] + delta[rows[r]], r < n; x is not written. */
 int umbs_add_rms_norm(int dtype, float* x, const float* delta, const int32_t* rows, int n, const float* w, float w_offset,
                       int width, float eps, void* y, float* copy, umbs_stream_t stream);
+
+/* A block's output waiting to be added to the residual stream: (delta + sum_k sel_w[t, k] pair_out[pair_pos[t, k]] +
+ * shared[t] shared_gate[t]) * scale * mult.  Every pointer may be NULL (shared_gate NULL: 1; scale NULL: 1). */
+typedef struct {
+    const float* delta;        /* fp32 [n, width] */
+    const float* pair_out;     /* fp32 [n top, width]: the routed experts' outputs in sorted-pair order */
+    const float* sel_w;        /* fp32 [n, top] */
+    const int32_t* pair_pos;   /* [n, top] */
+    int top;
+    const float* shared;       /* fp32 [n, width] */
+    const float* shared_gate;  /* fp32 [n] */
+    const float* scale;        /* fp32 [width] */
+    float mult;
+} umbs_delta_t;
+
+/* umbs_add_rms_norm for any pending output and either norm: x[t] += pending(t) (d may be NULL), copy, and
+ * y[t] = norm(x[t]) with kind = UMBS_NORM_* (b: the layer norm's bias).  rows != NULL: y[r] is the norm of
+ * x[rows[r]] + pending(rows[r]); x is not written.  width <= 8192. */
+int umbs_add_norm(int dtype, float* x, const umbs_delta_t* d, const int32_t* rows, int n, int kind, const float* w,
+                  const float* b, float w_offset, int width, float eps, void* y, float* copy, umbs_stream_t stream);
 
 /* z <- cap tanh(z / cap), fp32, n values. */
 int umbs_softcap(float* z, int64_t n, float cap, umbs_stream_t stream);
@@ -300,6 +390,9 @@ int umbs_mlstm(int dtype, const float* proj, int64_t ld, const float* gate_bias,
                float* o_scratch, float* seg_scratch, size_t seg_bytes, void* out, umbs_stream_t stream);
 
 int umbs_embedding(int dtype, const int32_t* ids, const void* table, float* y, int n, int width, umbs_stream_t stream);
+/* y[t] = table[ids[t]] * scale (fp32). */
+int umbs_embedding_scaled(int dtype, const int32_t* ids, const void* table, float scale, float* y, int n, int width,
+                          umbs_stream_t stream);
 
 #ifdef __cplusplus
 }

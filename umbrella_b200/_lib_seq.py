@@ -18,7 +18,9 @@ LIB_PATH = os.path.join(HERE, "libumbrella_b200_seq.so")
 UMBS_BF16, UMBS_F32 = 0, 1
 UMBS_MIX_RETENTION, UMBS_MIX_LATENT_ATTENTION, UMBS_MIX_CACHED_ATTENTION, UMBS_MIX_MLSTM = 0, 1, 2, 3
 UMBS_FORM_PARALLEL, UMBS_FORM_PRENORM = 0, 1
-UMBS_ACT_CLAMPED_GLU, UMBS_ACT_GELU_TANH = 1, 2
+UMBS_ACT_CLAMPED_GLU, UMBS_ACT_GELU_TANH, UMBS_ACT_SILU = 1, 2, 3
+UMBS_NORM_RMS, UMBS_NORM_LAYER = 0, 1
+UMBS_ROUTE_SOFTMAX_TOP, UMBS_ROUTE_SIGMOID_GROUPS = 0, 1
 UMBS_ATTN_SOFTMAX, UMBS_ATTN_SOFTMAX_SINK, UMBS_ATTN_SIGMOID = 0, 1, 2
 
 
@@ -32,7 +34,13 @@ class Batch(C.Structure):
 class Mlp(C.Structure):
     _fields_ = [("experts", c_int), ("top", c_int), ("ff", c_int), ("limit", c_float), ("w_router", c_void_p),
                 ("w_gu", c_void_p), ("w_down", c_void_p), ("shared_ff", c_int), ("shared_limit", c_float),
-                ("ws_gu", c_void_p), ("ws_down", c_void_p), ("act", c_int)]
+                ("ws_gu", c_void_p), ("ws_down", c_void_p), ("act", c_int), ("route_mode", c_int), ("groups", c_int),
+                ("keep", c_int), ("bias_gu", c_void_p), ("bias_down", c_void_p), ("w_shared_gate", c_void_p)]
+
+
+class Delta(C.Structure):
+    _fields_ = [("delta", c_void_p), ("pair_out", c_void_p), ("sel_w", c_void_p), ("pair_pos", c_void_p), ("top", c_int),
+                ("shared", c_void_p), ("shared_gate", c_void_p), ("scale", c_void_p), ("mult", c_float)]
 
 
 class Layer(C.Structure):
@@ -47,13 +55,16 @@ class Layer(C.Structure):
                 ("kv_heads", c_int), ("attn_mode", c_int), ("gate_kind", c_int), ("values_are_keys", c_int), ("pool", c_int),
                 ("taps", c_int), ("rot_mag", c_float), ("gate_cap", c_float), ("bias_in", c_void_p), ("conv_w", c_void_p),
                 ("head_bias", c_void_p), ("out_norm_w", c_void_p), ("kv_cache", c_void_p), ("kv_len", c_int),
-                ("pool_cache", c_void_p), ("pool_len", c_int), ("conv_state", c_void_p), ("mlstm_state", c_void_p)]
+                ("pool_cache", c_void_p), ("pool_len", c_int), ("conv_state", c_void_p), ("mlstm_state", c_void_p),
+                ("norm_kind", c_int), ("norm_b", c_void_p), ("norm2_b", c_void_p), ("out_scale", c_void_p),
+                ("out_scale2", c_void_p), ("residual_mult", c_float), ("rope_dim", c_int), ("sink", c_void_p)]
 
 
 class Model(C.Structure):
     _fields_ = [("dtype", c_int), ("width", c_int), ("vocab", c_int), ("n_layers", c_int), ("norm_groups", c_int),
                 ("slots", c_int), ("norm_eps", c_float), ("embed", c_void_p), ("final_norm", c_void_p), ("head", c_void_p),
-                ("layers", C.POINTER(Layer)), ("norm_offset", c_float), ("logit_softcap", c_float)]
+                ("layers", C.POINTER(Layer)), ("norm_offset", c_float), ("logit_softcap", c_float),
+                ("embed_scale", c_float), ("norm_kind", c_int), ("final_norm_b", c_void_p)]
 
 
 _BP = C.POINTER(Batch)
@@ -65,6 +76,9 @@ SIGNATURES = {
     "umbs_forward": (c_int, [C.POINTER(Model), _BP, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "umbs_gemm": (c_int, [c_int, c_void_p, c_int64, c_int, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int, c_int,
                           c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p]),
+    "umbs_gemm_ex": (c_int, [c_int, c_void_p, c_int64, c_int, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int, c_int,
+                             c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int64, c_int,
+                             c_void_p]),
     "umbs_group_norm_shift": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, _BP, c_int, c_int, c_float,
                                       c_void_p, c_void_p, c_void_p]),
     "umbs_group_norm_rows": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p]),
@@ -74,16 +88,25 @@ SIGNATURES = {
                                  c_void_p]),
     "umbs_latent_attention": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, _BP, c_int, c_int, c_int, c_float,
                                       c_void_p, c_size_t, c_void_p, c_void_p]),
+    "umbs_latent_attention_ex": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, _BP, c_int, c_int, c_int, c_int, c_float,
+                                         c_int, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "umbs_latent_prep": (c_int, [c_int, c_void_p, c_int64, _BP, c_int, c_int, c_int, c_int, c_void_p, c_float, c_int, c_void_p,
+                                 c_float, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "umbs_window_attention_fits": (c_int, [c_int, c_int]),
     "umbs_window_attention": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, _BP, c_int, c_int,
                                       c_int, c_int, c_float, c_void_p, c_int64, c_void_p]),
     "umbs_ring_append": (c_int, [c_int, c_void_p, c_void_p, c_int, _BP, c_int, c_void_p]),
     "umbs_moe_route": (c_int, [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_void_p, c_void_p]),
+    "umbs_moe_route_ex": (c_int, [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "umbs_token_gate": (c_int, [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "umbs_depth_mix": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "umbs_add_rms_norm": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_float, c_int, c_float, c_void_p,
                                   c_void_p, c_void_p]),
+    "umbs_add_norm": (c_int, [c_int, c_void_p, C.POINTER(Delta), c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int,
+                              c_float, c_void_p, c_void_p, c_void_p]),
     "umbs_softcap": (c_int, [c_void_p, c_int64, c_float, c_void_p]),
     "umbs_attention_prep": (c_int, [c_int, c_void_p, c_int64, c_void_p, _BP, c_int, c_int, c_int, c_int, c_int, c_int,
                                     c_void_p, c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p]),
@@ -94,6 +117,7 @@ SIGNATURES = {
     "umbs_mlstm": (c_int, [c_int, c_void_p, c_int64, c_void_p, _BP, c_int, c_int, c_int, c_float, c_float, c_void_p,
                            c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "umbs_embedding": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "umbs_embedding_scaled": (c_int, [c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p]),
 }
 
 _lib = None

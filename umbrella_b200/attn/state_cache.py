@@ -6,7 +6,9 @@ Every live sequence owns one slot.  A slot holds, per layer,
     ``parity`` names and writes the other, then the parity flips);
   * retention layers: the state matrices, fp32 [heads, dim, vdim];
   * latent-attention layers: a ring of the last ``ring_len`` latents, [ring_len, kv_rank] in the activation dtype,
-    position p at row p mod ring_len (ring_len = the layer's window, capped by ``max_length`` when that is given);
+    position p at row p mod ring_len (ring_len = the layer's window, capped by ``max_length`` when that is given); a
+    layer whose keys carry a rotated part shared by all heads keeps it behind the latent, [ring_len, kv_rank + rope_dim];
+    a layer without a window keeps a row for every token up to ``capacity`` tokens, as cached attention does;
   * cached-attention layers: key | value rows per token, [kv_len, kv_heads (dim + vdim)] in the activation dtype,
     position p at row p mod kv_len -- with a window a ring of max(window, pool) rows, without one a row for every
     token up to ``capacity`` tokens (the cache reallocates with twice the capacity when a sequence outgrows it);
@@ -31,7 +33,8 @@ class SequenceStateCache:
         self.slots = 0
         # tokens per sequence that the growing parts (windowless key/value rows, pooled-block tables) hold
         self.capacity = int(max_length or capacity or 512)
-        self._growing = any(l.mixer == "cached_attention" and (l.window <= 0 or l.pool > 0) for l in spec.layers)
+        self._growing = any((l.mixer == "cached_attention" and (l.window <= 0 or l.pool > 0)) or
+                            (l.mixer == "latent_attention" and l.window <= 0) for l in spec.layers)
         n = len(spec.layers)
         self.kv_cache: list[torch.Tensor | None] = [None] * n
         self.pool_cache: list[torch.Tensor | None] = [None] * n
@@ -47,7 +50,10 @@ class SequenceStateCache:
         self.grow(max(1, int(slots)))
 
     def ring_len(self, layer) -> int:
+        """Rows of a latent-attention layer's ring per slot: its window, or -- without one -- a row for every token."""
         n = int(layer.window)
+        if n <= 0:
+            return self.capacity
         return max(1, min(n, self.max_length) if self.max_length else n)
 
     def kv_len(self, layer) -> int:
@@ -93,8 +99,8 @@ class SequenceStateCache:
             if l.mixer == "retention":
                 self.ret_state[i] = widen(self.ret_state[i], (slots, l.heads, l.dim, l.vdim), 0, **f32)
             elif l.mixer == "latent_attention":
-                self.ring[i] = widen(self.ring[i], (slots, self.ring_len(l), l.kv_rank), 0, dtype=self.dtype,
-                                     device=self.device)
+                self.ring[i] = widen(self.ring[i], (slots, self.ring_len(l), l.kv_rank + getattr(l, "rope_dim", 0)), 0,
+                                     dtype=self.dtype, device=self.device)
             elif l.mixer == "cached_attention":
                 row = l.kv_heads * (l.dim + l.vdim)
                 self.kv_cache[i] = widen(self.kv_cache[i], (slots, self.kv_len(l), row), 0, **act)

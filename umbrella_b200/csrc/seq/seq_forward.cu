@@ -54,6 +54,7 @@ struct Scratch {
     float* gates;      // fp32 [T, max heads, 3]           mlstm: decay, input weight, floor per (token, head)
     float* ca_part;    // fp32 key-split partial sums of cached attention in decode steps
     size_t ca_part_bytes;
+    float* sgate;      // fp32 [T]  the shared expert's factor per token
 };
 
 static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratch* s) {
@@ -85,9 +86,12 @@ static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratc
             if (T >= 128 && ent * plane > segb) segb = ent * plane;
         }
         else {
-            up(in_rows, l.q_rank + l.kv_rank);
-            up(hmax, l.heads); up(qr, l.q_rank); up(kvr, l.kv_rank); up(hd, l.heads * l.dim); up(hkv, l.heads * l.kv_rank);
-            if (l.w_ukv != nullptr) up(hkvw, l.heads * (l.dim + l.vdim));
+            // (direct queries: q rows | latent | shared key part | gate rows; keys and queries carry rope_dim more numbers)
+            const int gate_rows = l.gate_kind == 2 ? l.heads * l.vdim : 0;
+            up(in_rows, l.q_rank > 0 ? l.q_rank + l.kv_rank : l.heads * (l.dim + l.rope_dim) + l.kv_rank + l.rope_dim + gate_rows);
+            up(hmax, l.heads); up(qr, l.q_rank); up(kvr, l.kv_rank + l.rope_dim); up(hd, l.heads * (l.dim + l.rope_dim));
+            up(hkv, l.heads * (l.kv_rank + l.rope_dim));
+            if (l.w_ukv != nullptr) up(hkvw, l.heads * (l.dim + l.rope_dim + l.vdim));
         }
         if (l.has_mlp) { up(top, l.mlp.top); up(experts, l.mlp.experts); up(ff, l.mlp.ff); up(sff, l.mlp.shared_ff); }
     }
@@ -126,6 +130,7 @@ static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratc
     z.gates = (float*)a.take(Tz * hall * 3 * 4);
     z.ca_part_bytes = (size_t)2048 * ((size_t)cav + 2) * 4;                 // (token, head, split) triples of a decode step
     z.ca_part = (float*)a.take(z.ca_part_bytes);
+    z.sgate = (float*)a.take(Tz * 4);
     if (s) *s = z;
     return a.used + 256;
 }
@@ -152,7 +157,7 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
     Scratch s;
     if (carve(m, T, b->n_want, (char*)workspace, &s) > workspace_bytes) return UMB_ERR_WORKSPACE;
     const int64_t plane = (int64_t)T * W;
-    UMBS_TRY(umbs_embedding(dt, b->tok_ids, m->embed, s.stack, T, W, stream));
+    UMBS_TRY(umbs_embedding_scaled(dt, b->tok_ids, m->embed, m->embed_scale != 0.f ? m->embed_scale : 1.f, s.stack, T, W, stream));
     const float* x = s.stack;                    // layer 0 reads X_0 itself
     bool prenorm = false;
     for (int i = 0; i < m->n_layers; ++i) {
@@ -161,12 +166,22 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
     }
     // Pre-norm layers: one fp32 residual stream, updated in place.  Every block's output waits in `pending` and is added
     // by the kernel that computes the next norm (or, behind the last layer, by the final norm).
-    const float* pending = nullptr;
+    umbs_delta_t pend{};
+    bool has_pend = false;
+    // the residual add + norm in front of a block: the plain RMS kernel where nothing else is asked for
+    auto norm_step = [&](const int32_t* rows, int n, int kind, const float* w, const float* bias, float off, void* y,
+                         float* copy) -> int {
+        const bool plain = kind == UMBS_NORM_RMS && (!has_pend || (pend.pair_out == nullptr && pend.shared == nullptr &&
+                                                                   pend.scale == nullptr && pend.mult == 1.f));
+        if (plain) return umbs_add_rms_norm(dt, s.stack, has_pend ? pend.delta : nullptr, rows, n, w, off, W, m->norm_eps, y, copy, stream);
+        return umbs_add_norm(dt, s.stack, has_pend ? &pend : nullptr, rows, n, kind, w, bias, off, W, m->norm_eps, y, copy, stream);
+    };
     for (int i = 0; prenorm && i < m->n_layers; ++i) {
         const umbs_layer_t& l = m->layers[i];
         const int hv = l.heads * l.vdim;
-        UMBS_TRY(umbs_add_rms_norm(dt, s.stack, pending, nullptr, T, l.norm_w, l.norm_offset, W, m->norm_eps, s.h,
-                                   (layer_out && i > 0) ? layer_out + (int64_t)(i - 1) * plane : nullptr, stream));
+        const float mult = l.residual_mult != 0.f ? l.residual_mult : 1.f;
+        UMBS_TRY(norm_step(nullptr, T, l.norm_kind, l.norm_w, l.norm_b, l.norm_offset, s.h,
+                           (layer_out && i > 0) ? layer_out + (int64_t)(i - 1) * plane : nullptr));
         if (l.mixer == UMBS_MIX_CACHED_ATTENTION) {
             const int cq = l.heads * l.dim, ck = l.kv_heads * l.dim, cv = l.values_are_keys ? 0 : l.kv_heads * l.vdim;
             const int gate_rows = l.gate_kind == 1 ? l.heads : (l.gate_kind == 2 ? hv : 0);
@@ -187,32 +202,71 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
             UMBS_TRY(umbs_gemm(dt, s.h, W, 0, l.w_in, W, 0, s.proj, rows, 0, 1, T, rows, W, 1, nullptr, nullptr, 0, 0.f, stream));
             UMBS_TRY(umbs_mlstm(dt, s.proj, rows, l.bias_in, b, l.heads, l.dim, l.vdim, l.gate_cap, m->norm_eps, l.out_norm_w,
                                 l.mlstm_state, s.gates, s.o32, s.seg_bytes ? s.seg : nullptr, s.seg_bytes, s.mixed, stream));
+        } else if (l.mixer == UMBS_MIX_LATENT_ATTENTION) {
+            // direct queries, keys through one normed latent per token plus a rotated part all heads share
+            if (l.q_rank != 0 || l.gate_kind == 1 || l.w_ukT == nullptr || l.w_uv == nullptr) return UMB_ERR_UNSUPPORTED;
+            const int Rt = l.rope_dim, hd1 = l.dim + Rt, hdq = l.heads * hd1, R = l.kv_rank, KD = R + Rt;
+            const int gate_rows = l.gate_kind == 2 ? hv : 0, rows = hdq + KD + gate_rows;
+            const float* gate = gate_rows ? s.proj + hdq + KD : nullptr;
+            UMBS_TRY(umbs_gemm(dt, s.h, W, 0, l.w_in, W, 0, s.proj, rows, 0, 1, T, rows, W, 1, nullptr, nullptr, 0, 0.f, stream));
+            UMBS_TRY(umbs_latent_prep(dt, s.proj, rows, b, l.heads, l.dim, Rt, R, l.kv_norm, m->norm_eps, l.rot_dims, l.inv_freq,
+                                      l.rot_mag, s.q, s.c, s.q_abs + R, KD, stream));
+            // q_abs[t, h, :R] = W_uk[h]^T q[t, h, :dim]: scores against the cached latents need no per-key up-projection;
+            // q_abs[t, h, R:] is the head's rotated part, written by the kernel above
+            UMBS_TRY(umbs_gemm(dt, s.q, hdq, hd1, l.w_ukT, l.dim, (int64_t)R * l.dim, s.q_abs, (int64_t)l.heads * KD, KD, 1, T, R,
+                               l.dim, l.heads, nullptr, nullptr, 0, 0.f, stream));
+            UMBS_TRY(umbs_latent_attention_ex(dt, s.q_abs, s.c, l.ring, l.ring_len, b, l.heads, R, Rt, l.window, l.scale,
+                                              l.attn_mode, l.sink, s.la_part, s.la_part_bytes, s.o_lat, stream));
+            UMBS_TRY(umbs_ring_append(dt, s.c, l.ring, l.ring_len, b, KD, stream));
+            // values per head from the weighted latents, times the sigmoid output gate
+            UMBS_TRY(umbs_gemm_ex(dt, s.o_lat, (int64_t)l.heads * R, R, l.w_uv, R, (int64_t)l.vdim * R, s.mixed, hv, l.vdim, 0, T,
+                                  l.vdim, R, l.heads, nullptr, nullptr, 0, 0.f, nullptr, gate, rows, l.vdim, stream));
         } else {
             return UMB_ERR_UNSUPPORTED;
         }
         UMBS_TRY(umbs_gemm(dt, s.mixed, hv, 0, l.w_o, hv, 0, s.mix_out, W, 0, 1, T, W, hv, 1, nullptr, nullptr, 0, 0.f, stream));
-        pending = s.mix_out;
+        pend = umbs_delta_t{};
+        pend.delta = s.mix_out; pend.scale = l.out_scale; pend.mult = mult;
+        has_pend = true;
         if (l.has_mlp) {
             const umbs_mlp_t& f = l.mlp;
-            if (f.experts > 0 || f.shared_ff <= 0 || l.norm2_w == nullptr) return UMB_ERR_UNSUPPORTED;   // dense feed-forward only
-            UMBS_TRY(umbs_add_rms_norm(dt, s.stack, pending, nullptr, T, l.norm2_w, l.norm_offset, W, m->norm_eps, s.h, nullptr,
-                                       stream));
-            UMBS_TRY(umbs_gemm(dt, s.h, W, 0, f.ws_gu, W, 0, s.ys, f.shared_ff, 0, 0, T, f.shared_ff, W, 1, nullptr, nullptr,
-                               f.act ? f.act : UMBS_ACT_CLAMPED_GLU, f.shared_limit, stream));
-            UMBS_TRY(umbs_gemm(dt, s.ys, f.shared_ff, 0, f.ws_down, f.shared_ff, 0, s.shared_out, W, 0, 1, T, W, f.shared_ff, 1,
-                               nullptr, nullptr, 0, 0.f, stream));
-            pending = s.shared_out;
+            if ((f.experts <= 0 && f.shared_ff <= 0) || l.norm2_w == nullptr) return UMB_ERR_UNSUPPORTED;
+            const int act = f.act ? f.act : UMBS_ACT_CLAMPED_GLU;
+            UMBS_TRY(norm_step(nullptr, T, l.norm_kind, l.norm2_w, l.norm2_b, l.norm_offset, s.h, nullptr));
+            pend = umbs_delta_t{};
+            pend.scale = l.out_scale2; pend.mult = mult;
+            if (f.experts > 0) {
+                UMBS_TRY(umbs_moe_route_ex(dt, s.h, T, W, f.w_router, f.experts, f.top, f.route_mode, f.groups, f.keep, s.sel_w,
+                                           s.grp_off, s.pair_tok, s.pair_pos, s.route_scratch, stream));
+                UMBS_TRY(umbs_gemm(dt, s.h, W, 0, f.w_gu, W, (int64_t)2 * f.ff * W, s.y, f.ff, 0, 0, T, f.ff, W, f.experts,
+                                   s.grp_off, s.pair_tok, act, f.limit, stream));
+                UMBS_TRY(umbs_gemm(dt, s.y, f.ff, 0, f.w_down, f.ff, (int64_t)W * f.ff, s.pair_out, W, 0, 1, T, W, f.ff, f.experts,
+                                   s.grp_off, nullptr, 0, 0.f, stream));
+                pend.pair_out = s.pair_out; pend.sel_w = s.sel_w; pend.pair_pos = s.pair_pos; pend.top = f.top;
+            }
+            if (f.shared_ff > 0) {
+                UMBS_TRY(umbs_gemm_ex(dt, s.h, W, 0, f.ws_gu, W, 0, s.ys, f.shared_ff, 0, 0, T, f.shared_ff, W, 1, nullptr, nullptr,
+                                      act, f.shared_limit, f.bias_gu, nullptr, 0, 0, stream));
+                UMBS_TRY(umbs_gemm_ex(dt, s.ys, f.shared_ff, 0, f.ws_down, f.shared_ff, 0, s.shared_out, W, 0, 1, T, W, f.shared_ff, 1,
+                                      nullptr, nullptr, 0, 0.f, f.bias_down, nullptr, 0, 0, stream));
+                if (f.w_shared_gate != nullptr) UMBS_TRY(umbs_token_gate(dt, s.h, T, W, f.w_shared_gate, s.sgate, stream));
+                if (f.experts > 0 || f.w_shared_gate != nullptr) {
+                    pend.shared = s.shared_out;
+                    pend.shared_gate = f.w_shared_gate != nullptr ? s.sgate : nullptr;
+                } else {
+                    pend.delta = s.shared_out;           // a dense feed-forward: the plain pending sum
+                }
+            }
         }
     }
     if (prenorm) {
         if (layer_out != nullptr) {              // the last layer's stream is asked for: finish the sum for every row
-            UMBS_TRY(umbs_add_rms_norm(dt, s.stack, pending, nullptr, T, nullptr, 0.f, W, m->norm_eps, nullptr,
-                                       layer_out + (int64_t)(m->n_layers - 1) * plane, stream));
-            pending = nullptr;
+            UMBS_TRY(norm_step(nullptr, T, UMBS_NORM_RMS, nullptr, nullptr, 0.f, nullptr, layer_out + (int64_t)(m->n_layers - 1) * plane));
+            has_pend = false;
         }
         if (logits != nullptr && b->n_want > 0) {
-            UMBS_TRY(umbs_add_rms_norm(dt, s.stack, pending, b->want_rows, b->n_want, m->final_norm, m->norm_offset, W,
-                                       m->norm_eps, s.final_h, nullptr, stream));
+            UMBS_TRY(norm_step(b->want_rows, b->n_want, m->norm_kind, m->final_norm, m->final_norm_b, m->norm_offset, s.final_h,
+                               nullptr));
             UMBS_TRY(umbs_gemm(dt, s.final_h, W, 0, m->head, W, 0, logits, m->vocab, 0, 1, b->n_want, m->vocab, W, 1, nullptr,
                                nullptr, 0, 0.f, stream));
             if (m->logit_softcap > 0.f) UMBS_TRY(umbs_softcap(logits, (int64_t)b->n_want * m->vocab, m->logit_softcap, stream));

@@ -27,6 +27,10 @@ struct GemmArgs {
     const int32_t* row_src;
     float limit;
     int act;          // UMBS_ACT_*: which gated activation a dual product applies
+    const float* bias;       // fp32 [N] (dual: [2 N]) added to the sums, or NULL
+    const float* out_gate;   // fp32: the result is multiplied by sigmoid(out_gate[row ld_gate + g gate_goff + n]), or NULL
+    int64_t ld_gate;
+    int gate_goff;
 };
 
 __device__ __forceinline__ float gated_act(float g, float u, float limit, int act) {
@@ -34,9 +38,22 @@ __device__ __forceinline__ float gated_act(float g, float u, float limit, int ac
         const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
         return 0.5f * g * (1.f + tanhf(z)) * u;
     }
+    if (act == UMBS_ACT_SILU) return g * (1.f / (1.f + expf(-g))) * u;
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
     return g * (1.f / (1.f + expf(-1.702f * g))) * (u + 1.f);
+}
+
+// What every kernel does with a finished sum (and, for a gate|up pair, its partner): bias, activation, output gate.
+template <bool DUAL>
+__device__ __forceinline__ float finish(const GemmArgs& a, float s, float s2, int g, int64_t row, int n) {
+    if (a.bias != nullptr) {
+        s += a.bias[n];
+        if (DUAL) s2 += a.bias[a.N + n];
+    }
+    float v = DUAL ? gated_act(s, s2, a.limit, a.act) : s;
+    if (a.out_gate != nullptr) v *= 1.f / (1.f + expf(-a.out_gate[row * a.ld_gate + (int64_t)g * a.gate_goff + n]));
+    return v;
 }
 
 // ------------------------------------------------------------------------------------------------ SIMT
@@ -100,7 +117,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(GemmArgs a) {
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
             if (n >= a.N) continue;
-            const float v = DUAL ? gated_act(acc[i][j], acc2[DUAL ? i : 0][j], a.limit, a.act) : acc[i][j];
+            const float v = finish<DUAL>(a, acc[i][j], acc2[DUAL ? i : 0][j], g, row_lo + m, n);
             C[(int64_t)(row_lo + m) * a.ldc + n] = from_f32<TC>(v);
         }
     }
@@ -211,7 +228,7 @@ __global__ void __launch_bounds__(256) gemm_mma_kernel(GemmArgs a) {
             for (int e = 0; e < 4; ++e) {
                 const int m = m0 + wm + 16 * i + gr + (e >> 1) * 8, n = n0 + wn + 8 * j + gc + (e & 1);
                 if (m >= rows || n >= a.N) continue;
-                const float v = DUAL ? gated_act(acc[i][j][e], acc2[DUAL ? i : 0][j][e], a.limit, a.act) : acc[i][j][e];
+                const float v = finish<DUAL>(a, acc[i][j][e], acc2[DUAL ? i : 0][j][e], g, row_lo + m, n);
                 C[(int64_t)(row_lo + m) * a.ldc + n] = from_f32<TC>(v);
             }
 }
@@ -291,7 +308,7 @@ __global__ void __launch_bounds__(32 * SK_WARPS) gemm_skinny_kernel(GemmArgs a) 
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
                 if (m0 + m >= rows) continue;
-                const float v = DUAL ? gated_act(acc[2 * o][m], acc[DUAL ? 2 * o + 1 : o][m], a.limit, a.act) : acc[o][m];
+                const float v = finish<DUAL>(a, DUAL ? acc[2 * o][m] : acc[o][m], acc[DUAL ? 2 * o + 1 : o][m], g, row_lo + m0 + m, n0 + o);
                 C[(int64_t)(row_lo + m0 + m) * a.ldc + n0 + o] = from_f32<TC>(v);
             }
         }
@@ -335,11 +352,20 @@ using namespace umbs;
 extern "C" int umbs_gemm(int dtype, const void* A, int64_t lda, int a_goff, const void* W, int64_t ldw, int64_t w_gstride,
                          void* C, int64_t ldc, int c_goff, int c_f32, int M, int N, int K, int groups,
                          const int32_t* grp_off, const int32_t* row_src, int dual, float limit, umbs_stream_t stream) {
+    return umbs_gemm_ex(dtype, A, lda, a_goff, W, ldw, w_gstride, C, ldc, c_goff, c_f32, M, N, K, groups, grp_off, row_src, dual,
+                        limit, nullptr, nullptr, 0, 0, stream);
+}
+
+extern "C" int umbs_gemm_ex(int dtype, const void* A, int64_t lda, int a_goff, const void* W, int64_t ldw, int64_t w_gstride,
+                            void* C, int64_t ldc, int c_goff, int c_f32, int M, int N, int K, int groups,
+                            const int32_t* grp_off, const int32_t* row_src, int dual, float limit, const float* bias,
+                            const float* out_gate, int64_t ld_gate, int gate_goff, umbs_stream_t stream) {
     if (M <= 0 || N <= 0 || groups <= 0) return 0;
     if (K <= 0 || A == nullptr || W == nullptr || C == nullptr) return UMB_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     GemmArgs a{A, lda, a_goff, W, ldw, w_gstride, C, ldc, c_goff, M, N, K, grp_off, row_src, limit,
-               dual == UMBS_ACT_GELU_TANH ? UMBS_ACT_GELU_TANH : UMBS_ACT_CLAMPED_GLU};
+               (dual == UMBS_ACT_GELU_TANH || dual == UMBS_ACT_SILU) ? dual : UMBS_ACT_CLAMPED_GLU,
+               bias, out_gate, ld_gate, gate_goff};
     if (dtype == UMBS_F32) {
         launch_simt<float, float>(a, groups, dual != 0, st);          // activations are fp32 too: c_f32 changes nothing
     } else if (dtype == UMBS_BF16) {

@@ -41,10 +41,10 @@ __device__ float block_sum(float v, float* red) {   // red: >= 33 floats of shar
 // ------------------------------------------------------------------------------------------------ embedding
 template <typename T>
 __global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table, float* __restrict__ y,
-                                 int width) {
+                                 int width, float scale) {
     const int t = blockIdx.x;
     const T* row = table + (int64_t)ids[t] * width;
-    for (int e = threadIdx.x; e < width; e += blockDim.x) y[(int64_t)t * width + e] = to_f32(row[e]);
+    for (int e = threadIdx.x; e < width; e += blockDim.x) y[(int64_t)t * width + e] = to_f32(row[e]) * scale;
 }
 
 // ------------------------------------------------------------------------------------------------ group norm (+ shift)
@@ -368,10 +368,12 @@ __device__ __forceinline__ void unpack16(const uint4& v, float* dst, const __nv_
 template <typename T, int RPL>
 __global__ void __launch_bounds__(256) latent_attention_kernel(const float* __restrict__ q_abs, const T* __restrict__ c,
                                                                const T* __restrict__ ring, int ring_len, Batch b, int heads,
-                                                               int R, int window, float scale, int rpb, int vec,
-                                                               int nsplit, float* __restrict__ part, T* __restrict__ out) {
+                                                               int R, int KD, int window, float scale, int rpb, int vec,
+                                                               int nsplit, int use_sink, const float* __restrict__ sink,
+                                                               float* __restrict__ part, T* __restrict__ out) {
+    // A key row holds KD >= R numbers: the latent (R, which is also the value) and a part all heads share; q_abs rows likewise.
     extern __shared__ __align__(16) float sm[];
-    const int RS = ((R + 3) & ~3) + 4;                 // row stride: 16-byte rows, lanes 4 banks apart
+    const int RS = ((KD + 3) & ~3) + 4;                // row stride: 16-byte rows, lanes 4 banks apart
     float* qs = sm;                                    // [32][RS]
     float* cs = sm + (size_t)kLaRows * RS;             // [32][RS]
     const int s = blockIdx.y;
@@ -379,12 +381,12 @@ __global__ void __launch_bounds__(256) latent_attention_kernel(const float* __re
     const int row0 = blockIdx.x * rpb, nrows = min(len * heads, row0 + rpb);
     if (row0 >= nrows) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const T* rbase = ring + (int64_t)slot * ring_len * R;
-    // queries of the block's rows, zero beyond R and beyond the sequence
+    const T* rbase = ring + (int64_t)slot * ring_len * KD;
+    // queries of the block's rows, zero beyond KD and beyond the sequence
     for (int i = threadIdx.x; i < kLaRows * RS; i += blockDim.x) {
         const int rr = i / RS, r = i - rr * RS, row = row0 + rr;
         float v = 0.f;
-        if (row < nrows && r < R) v = q_abs[((int64_t)(start + row / heads) * heads + row % heads) * R + r];
+        if (row < nrows && r < KD) v = q_abs[((int64_t)(start + row / heads) * heads + row % heads) * KD + r];
         qs[i] = v;
     }
     int rpos[kLaQH];                                    // position of each of the warp's rows, -1 = no such row
@@ -395,6 +397,10 @@ __global__ void __launch_bounds__(256) latent_attention_kernel(const float* __re
         rpos[a] = row < nrows ? pos0 + row / heads : -1;
         m[a] = -INFINITY;
         l[a] = 0.f;
+        if (use_sink && nsplit == 1 && row < nrows) {      // the sink: a score without a key that counts once in the sum
+            m[a] = sink ? sink[row % heads] : 0.f;
+            l[a] = 1.f;
+        }
 #pragma unroll
         for (int i = 0; i < RPL; ++i) acc[a][i] = 0.f;
     }
@@ -411,26 +417,26 @@ __global__ void __launch_bounds__(256) latent_attention_kernel(const float* __re
         if (vec) {
             // 16-byte pieces, every thread's loads of the tile in flight together
             constexpr int EP = 16 / sizeof(T);
-            const int ppr = R / EP, pieces = kLaKeys * ppr;
+            const int ppr = KD / EP, pieces = kLaKeys * ppr;
 #pragma unroll 4
             for (int i = threadIdx.x; i < pieces; i += 256) {
                 const int kk = i / ppr, e0 = (i - kk * ppr) * EP, j = j0 + kk;
                 uint4 v = make_uint4(0, 0, 0, 0);
                 if (j <= pos_last) {
-                    const T* src = j >= pos0 ? c + (int64_t)(start + j - pos0) * R : rbase + (int64_t)(j % ring_len) * R;
+                    const T* src = j >= pos0 ? c + (int64_t)(start + j - pos0) * KD : rbase + (int64_t)(j % ring_len) * KD;
                     v = *reinterpret_cast<const uint4*>(src + e0);
                 }
                 unpack16(v, cs + kk * RS + e0, (const T*)nullptr);
             }
             if (threadIdx.x < kLaKeys) {
-                for (int r = R; r < RS; ++r) cs[threadIdx.x * RS + r] = 0.f;
+                for (int r = KD; r < RS; ++r) cs[threadIdx.x * RS + r] = 0.f;
             }
         } else {
             for (int kk = warp; kk < kLaKeys; kk += 8) {
                 const int j = j0 + kk;
                 const T* src = nullptr;
-                if (j <= pos_last) src = j >= pos0 ? c + (int64_t)(start + j - pos0) * R : rbase + (int64_t)(j % ring_len) * R;
-                for (int r = lane; r < RS; r += 32) cs[kk * RS + r] = (src != nullptr && r < R) ? to_f32(src[r]) : 0.f;
+                if (j <= pos_last) src = j >= pos0 ? c + (int64_t)(start + j - pos0) * KD : rbase + (int64_t)(j % ring_len) * KD;
+                for (int r = lane; r < RS; r += 32) cs[kk * RS + r] = (src != nullptr && r < KD) ? to_f32(src[r]) : 0.f;
             }
         }
         __syncthreads();
@@ -442,7 +448,7 @@ __global__ void __launch_bounds__(256) latent_attention_kernel(const float* __re
         float sc[kLaQH] = {};
         const float4* ck = reinterpret_cast<const float4*>(cs + lane * RS);
         const float4* q4 = reinterpret_cast<const float4*>(qs + warp * kLaQH * RS);
-        const int n4 = (R + 3) >> 2, rs4 = RS >> 2;
+        const int n4 = (KD + 3) >> 2, rs4 = RS >> 2;
         for (int r = 0; r < n4; ++r) {
             const float4 cv = ck[r];
 #pragma unroll
@@ -513,15 +519,17 @@ __global__ void __launch_bounds__(256) latent_attention_kernel(const float* __re
 // are worked out once into shared memory; then every thread owns latent components and adds the splits in order
 // (independent loads, so they overlap).
 template <typename T>
-__global__ void latent_merge_kernel(const float* __restrict__ part, int nsplit, int R, T* __restrict__ out) {
+__global__ void latent_merge_kernel(const float* __restrict__ part, int nsplit, int R, int heads, int use_sink,
+                                    const float* __restrict__ sink, T* __restrict__ out) {
     extern __shared__ float wgt[];         // [nsplit]
     const int row = blockIdx.x;
     const float* p = part + (int64_t)row * nsplit * (R + 2);
     if (threadIdx.x < 32) {
-        float mx = -INFINITY;
+        const float sk = sink ? sink[row % heads] : 0.f;
+        float mx = use_sink ? sk : -INFINITY;
         for (int i = threadIdx.x; i < nsplit; i += 32) mx = fmaxf(mx, p[(int64_t)i * (R + 2)]);
         mx = warp_max(mx);
-        float den = 0.f;
+        float den = (use_sink && threadIdx.x == 0) ? expf(sk - mx) : 0.f;
         for (int i = threadIdx.x; i < nsplit; i += 32) {
             const float mi = p[(int64_t)i * (R + 2)];
             const float e = mi > -INFINITY ? expf(mi - mx) : 0.f;
@@ -563,8 +571,45 @@ __device__ __forceinline__ float router_logit(const T* __restrict__ hr, const fl
 }
 
 // `top` rounds of arg-max over z (lowest index wins a tie; z is consumed) and the softmax over the chosen logits.
-__device__ __forceinline__ void route_choose(float* z, int experts, int top, float* __restrict__ w_out,
-                                             int32_t* __restrict__ e_out, int32_t* counts) {
+// UMBS_ROUTE_SIGMOID_GROUPS: z becomes sigmoid(z); a group's score is the sum of its two largest scores; `keep` rounds of
+// arg-max over the groups mark the eligible ones; `top` rounds of arg-max over the eligible scores; weights = score / sum.
+__device__ __forceinline__ void route_choose(float* z, int experts, int top, int mode, int groups, int keep,
+                                             float* __restrict__ w_out, int32_t* __restrict__ e_out, int32_t* counts) {
+    if (mode == UMBS_ROUTE_SIGMOID_GROUPS) {
+        const int per = experts / groups;
+        for (int e = 0; e < experts; ++e) z[e] = 1.f / (1.f + expf(-z[e]));
+        unsigned long long kept = 0ull;
+        for (int r = 0; r < keep; ++r) {
+            int best = -1;
+            float bv = -INFINITY;
+            for (int g = 0; g < groups; ++g) {
+                if ((kept >> g) & 1ull) continue;
+                float a = -INFINITY, b2 = -INFINITY;                   // the group's two largest scores
+                for (int e = g * per; e < (g + 1) * per; ++e) {
+                    const float v = z[e];
+                    if (v > a) { b2 = a; a = v; }
+                    else if (v > b2) b2 = v;
+                }
+                const float gs = per > 1 ? a + b2 : a;
+                if (gs > bv) { bv = gs; best = g; }
+            }
+            if (best >= 0) kept |= 1ull << best;
+        }
+        float den = 0.f;
+        for (int k = 0; k < top; ++k) {
+            int best = -1;
+            float bv = -INFINITY;
+            for (int e = 0; e < experts; ++e)
+                if (((kept >> (e / per)) & 1ull) && z[e] > bv) { bv = z[e]; best = e; }
+            e_out[k] = best;
+            w_out[k] = bv;
+            den += bv;
+            z[best] = -INFINITY;
+            atomicAdd(counts + best, 1);
+        }
+        for (int k = 0; k < top; ++k) w_out[k] /= (den + 1e-20f);
+        return;
+    }
     float zmax = 0.f, den = 0.f;
     for (int k = 0; k < top; ++k) {
         int best = 0;
@@ -585,8 +630,9 @@ __device__ __forceinline__ void route_choose(float* z, int experts, int top, flo
 // One block per token: the warps share the experts' logits, then one thread chooses.
 template <typename T>
 __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ h, int n, int width, const float* __restrict__ wr,
-                                                         int experts, int top, float* __restrict__ sel_w,
-                                                         int32_t* __restrict__ sel_e, int32_t* __restrict__ counts) {
+                                                         int experts, int top, int mode, int groups, int keep,
+                                                         float* __restrict__ sel_w, int32_t* __restrict__ sel_e,
+                                                         int32_t* __restrict__ counts) {
     extern __shared__ float z[];           // [experts]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int t = blockIdx.x;
@@ -596,7 +642,8 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ h
         if (lane == 0) z[e] = s;
     }
     __syncthreads();
-    if (threadIdx.x == 0) route_choose(z, experts, top, sel_w + (int64_t)t * top, sel_e + (int64_t)t * top, counts);
+    if (threadIdx.x == 0)
+        route_choose(z, experts, top, mode, groups, keep, sel_w + (int64_t)t * top, sel_e + (int64_t)t * top, counts);
 }
 
 // The whole routing of a small step (a decode step) in one block: logits of every (token, expert) pair, the choice per
@@ -605,6 +652,7 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ h
 template <typename T>
 __global__ void __launch_bounds__(1024) moe_route_small_kernel(const T* __restrict__ h, int n, int width,
                                                               const float* __restrict__ wr, int experts, int top,
+                                                              int mode, int groups, int keep,
                                                               float* __restrict__ sel_w, int32_t* __restrict__ sel_e,
                                                               int32_t* __restrict__ grp_off, int32_t* __restrict__ pair_tok,
                                                               int32_t* __restrict__ pair_pos) {
@@ -621,7 +669,7 @@ __global__ void __launch_bounds__(1024) moe_route_small_kernel(const T* __restri
     }
     __syncthreads();
     for (int t = threadIdx.x; t < n; t += blockDim.x)
-        route_choose(zs + t * experts, experts, top, sel_w + (int64_t)t * top, chosen + t * top, counts);
+        route_choose(zs + t * experts, experts, top, mode, groups, keep, sel_w + (int64_t)t * top, chosen + t * top, counts);
     __syncthreads();
     if (threadIdx.x == 0) {
         int s = 0;
@@ -656,6 +704,15 @@ __global__ void moe_scatter_kernel(const int32_t* __restrict__ sel_e, int n_pair
     const int p = grp_off[e] + atomicAdd(cursor + e, 1);
     pair_tok[p] = i / top;
     pair_pos[i] = p;
+}
+
+// One warp per token: g[t] = sigmoid(w . h[t]).
+template <typename T>
+__global__ void token_gate_kernel(const T* __restrict__ h, int n, int width, const float* __restrict__ w, float* __restrict__ g) {
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= n) return;
+    const float s = router_logit(h + (int64_t)t * width, w, width, threadIdx.x & 31);
+    if ((threadIdx.x & 31) == 0) g[t] = 1.f / (1.f + expf(-s));
 }
 
 // ------------------------------------------------------------------------------------------------ residual + depth mix
@@ -705,9 +762,23 @@ static inline int threads_for(int width) { return width >= 1024 ? 256 : (width >
 
 extern "C" int umbs_embedding(int dtype, const int32_t* ids, const void* table, float* y, int n, int width,
                               umbs_stream_t stream) {
+    return umbs_embedding_scaled(dtype, ids, table, 1.f, y, n, width, stream);
+}
+
+extern "C" int umbs_embedding_scaled(int dtype, const int32_t* ids, const void* table, float scale, float* y, int n, int width,
+                                     umbs_stream_t stream) {
     if (n <= 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
-    UMBS_DISPATCH_T(dtype, embedding_kernel<T><<<n, threads_for(width), 0, st>>>(ids, (const T*)table, y, width));
+    UMBS_DISPATCH_T(dtype, embedding_kernel<T><<<n, threads_for(width), 0, st>>>(ids, (const T*)table, y, width, scale));
+    count_launches(1);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int umbs_token_gate(int dtype, const void* h, int n, int width, const float* w, float* g, umbs_stream_t stream) {
+    if (n <= 0) return 0;
+    if (h == nullptr || w == nullptr || g == nullptr) return UMB_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    UMBS_DISPATCH_T(dtype, token_gate_kernel<T><<<(n + 3) / 4, 128, 0, st>>>((const T*)h, n, width, w, g));
     count_launches(1);
     return (int)cudaGetLastError();
 }
@@ -825,10 +896,11 @@ extern "C" int umbs_latent_norm(int dtype, const float* x, int n, int q_rank, in
 
 template <typename T>
 static int launch_latent_attention(const float* q_abs, const void* c, const void* ring, int ring_len, const Batch& b,
-                                   int heads, int R, int window, float scale, float* part, size_t part_bytes, void* out,
-                                   cudaStream_t st) {
+                                   int heads, int R, int KD, int window, float scale, int use_sink, const float* sink,
+                                   float* part, size_t part_bytes, void* out, cudaStream_t st) {
     const int rpb = kLaRows;
-    const size_t smem = (size_t)2 * kLaRows * (((R + 3) & ~3) + 4) * sizeof(float);
+    const size_t smem = (size_t)2 * kLaRows * (((KD + 3) & ~3) + 4) * sizeof(float);
+    if (smem > (size_t)200 * 1024) return UMB_ERR_UNSUPPORTED;
     // decode steps: few blocks and a long serial walk over the window -> split the keys over as many blocks per row tile
     // as fill the GPU (as many block slots per SM as the tiles' shared memory allows), as far as the scratch buffer reaches
     int nsplit = 1;
@@ -841,7 +913,7 @@ static int launch_latent_attention(const float* q_abs, const void* c, const void
         nsplit = (int)std::max<size_t>(1, std::min<size_t>(nsplit, fit));
     }
     const int ep = 16 / (int)sizeof(T);
-    const int vec = (R % ep == 0) && ((uintptr_t)c % 16 == 0) && ((uintptr_t)ring % 16 == 0);
+    const int vec = (KD % ep == 0) && ((uintptr_t)c % 16 == 0) && ((uintptr_t)ring % 16 == 0);
     const dim3 grid((b.max_seq_len * heads + rpb - 1) / rpb, b.n_seqs, nsplit), block(256);
 #define UMBS_LA(RPL)                                                                                                   \
     do {                                                                                                               \
@@ -853,8 +925,8 @@ static int launch_latent_attention(const float* q_abs, const void* c, const void
             set = smem;                                                                                                \
         }                                                                                                              \
         latent_attention_kernel<T, RPL><<<grid, block, smem, st>>>(q_abs, (const T*)c, (const T*)ring, ring_len, b,    \
-                                                                   heads, R, window, scale, rpb, vec, nsplit, part,    \
-                                                                   (T*)out);                                           \
+                                                                   heads, R, KD, window, scale, rpb, vec, nsplit,      \
+                                                                   use_sink, sink, part, (T*)out);                     \
     } while (0)
     if (R <= 32) UMBS_LA(1);
     else if (R <= 64) UMBS_LA(2);
@@ -865,7 +937,7 @@ static int launch_latent_attention(const float* q_abs, const void* c, const void
 #undef UMBS_LA
     if (nsplit > 1) {
         const int rows = b.n_tokens * heads;
-        latent_merge_kernel<T><<<rows, R >= 256 ? 256 : (R >= 128 ? 128 : 64), nsplit * sizeof(float), st>>>(part, nsplit, R, (T*)out);
+        latent_merge_kernel<T><<<rows, R >= 256 ? 256 : (R >= 128 ? 128 : 64), nsplit * sizeof(float), st>>>(part, nsplit, R, heads, use_sink, sink, (T*)out);
         count_launches(1);
     }
     return 0;
@@ -874,11 +946,23 @@ static int launch_latent_attention(const float* q_abs, const void* c, const void
 extern "C" int umbs_latent_attention(int dtype, const float* q_abs, const void* c, const void* ring, int ring_len,
                                      const umbs_batch_t* batch, int heads, int kv_rank, int window, float scale,
                                      float* split_scratch, size_t split_bytes, void* out, umbs_stream_t stream) {
+    if (window < 1) return UMB_ERR_ARG;
+    return umbs_latent_attention_ex(dtype, q_abs, c, ring, ring_len, batch, heads, kv_rank, 0, window, scale, UMBS_ATTN_SOFTMAX,
+                                    nullptr, split_scratch, split_bytes, out, stream);
+}
+
+extern "C" int umbs_latent_attention_ex(int dtype, const float* q_abs, const void* c, const void* ring, int ring_len,
+                                        const umbs_batch_t* batch, int heads, int kv_rank, int rope_dim, int window,
+                                        float scale, int mode, const float* sink, float* split_scratch, size_t split_bytes,
+                                        void* out, umbs_stream_t stream) {
     if (batch->n_tokens <= 0) return 0;
-    if (window < 1 || ring_len < 1) return UMB_ERR_ARG;
+    if (ring_len < 1 || rope_dim < 0 || kv_rank < 1 || heads < 1) return UMB_ERR_ARG;
+    if (mode != UMBS_ATTN_SOFTMAX && mode != UMBS_ATTN_SOFTMAX_SINK) return UMB_ERR_UNSUPPORTED;
+    if (window <= 0) window = 1 << 30;                       // every earlier token
     int rc = 0;
-    UMBS_DISPATCH_T(dtype, rc = launch_latent_attention<T>(q_abs, c, ring, ring_len, *batch, heads, kv_rank, window, scale,
-                                                           split_scratch, split_bytes, out, (cudaStream_t)stream));
+    UMBS_DISPATCH_T(dtype, rc = launch_latent_attention<T>(q_abs, c, ring, ring_len, *batch, heads, kv_rank, kv_rank + rope_dim,
+                                                           window, scale, mode == UMBS_ATTN_SOFTMAX_SINK, sink, split_scratch,
+                                                           split_bytes, out, (cudaStream_t)stream));
     if (rc) return rc;
     count_launches(1);
     return (int)cudaGetLastError();
@@ -897,15 +981,28 @@ extern "C" int umbs_ring_append(int dtype, const void* c, void* ring, int ring_l
 extern "C" int umbs_moe_route(int dtype, const void* h, int n, int width, const float* w_router, int experts, int top,
                               float* sel_w, int32_t* grp_off, int32_t* pair_tok, int32_t* pair_pos, int32_t* scratch,
                               umbs_stream_t stream) {
+    return umbs_moe_route_ex(dtype, h, n, width, w_router, experts, top, UMBS_ROUTE_SOFTMAX_TOP, 1, 1, sel_w, grp_off, pair_tok,
+                             pair_pos, scratch, stream);
+}
+
+extern "C" int umbs_moe_route_ex(int dtype, const void* h, int n, int width, const float* w_router, int experts, int top,
+                                 int mode, int groups, int keep, float* sel_w, int32_t* grp_off, int32_t* pair_tok,
+                                 int32_t* pair_pos, int32_t* scratch, umbs_stream_t stream) {
     if (n <= 0) return 0;
     if (top < 1 || top > experts) return UMB_ERR_ARG;
+    if (mode == UMBS_ROUTE_SIGMOID_GROUPS) {
+        if (groups < 1 || experts % groups != 0 || keep < 1 || keep > groups || top > keep * (experts / groups)) return UMB_ERR_ARG;
+        if (groups > 64) return UMB_ERR_UNSUPPORTED;
+    } else if (mode != UMBS_ROUTE_SOFTMAX_TOP) {
+        return UMB_ERR_ARG;
+    }
     cudaStream_t st = (cudaStream_t)stream;
     if ((size_t)n * experts <= 256 && (size_t)n * top <= 1024) {
         // a small step (decoding): one block does the logits, the choice, the offsets and the sorted pair list
         const size_t smem = ((size_t)n * experts + 2 * (size_t)experts + 1 + (size_t)n * top) * sizeof(float);
         UMBS_DISPATCH_T(dtype, moe_route_small_kernel<T><<<1, 1024, smem, st>>>((const T*)h, n, width, w_router, experts, top,
-                                                                              sel_w, scratch + 2 * experts, grp_off, pair_tok,
-                                                                              pair_pos));
+                                                                              mode, groups, keep, sel_w, scratch + 2 * experts,
+                                                                              grp_off, pair_tok, pair_pos));
         count_launches(1);
         return (int)cudaGetLastError();
     }
@@ -916,7 +1013,7 @@ extern "C" int umbs_moe_route(int dtype, const void* h, int n, int width, const 
     if (e != cudaSuccess) return (int)e;
     const int rthreads = experts >= 8 ? 256 : 32 * experts;
     UMBS_DISPATCH_T(dtype, moe_router_kernel<T><<<n, rthreads, (size_t)experts * sizeof(float), st>>>(
-                               (const T*)h, n, width, w_router, experts, top, sel_w, sel_e, counts));
+                               (const T*)h, n, width, w_router, experts, top, mode, groups, keep, sel_w, sel_e, counts));
     moe_offsets_kernel<<<1, 32, 0, st>>>(counts, experts, grp_off, cursor);
     const int pairs = n * top;
     moe_scatter_kernel<<<(pairs + 255) / 256, 256, 0, st>>>(sel_e, pairs, top, grp_off, cursor, pair_tok, pair_pos);

@@ -75,6 +75,129 @@ __global__ void add_rms_norm_kernel(float* __restrict__ x, const float* __restri
     }
 }
 
+// Residual add + norm for any pending block output (dense, routed experts' pairs, gated shared expert; layer scale and
+// residual multiplier) and either norm.  One block per row, the row in registers (8 values per thread); sums in a fixed
+// tree, so a row's result does not depend on what else is in the step.  The layer norm takes its mean first and the mean
+// of the squared deviations second.
+__device__ __forceinline__ float block_sum_pn(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum_pn(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float s = lane < nw ? red[lane] : 0.f;
+        s = warp_sum_pn(s);
+        if (lane == 0) red[32] = s;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+template <typename T>
+__global__ void add_norm_kernel(float* __restrict__ x, umbs_delta_t d, int has_d, const int32_t* __restrict__ rows, int kind,
+                                const float* __restrict__ w, const float* __restrict__ bias, float w_offset, int width, float eps,
+                                T* __restrict__ y, float* __restrict__ copy) {
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const int64_t src = rows ? rows[r] : r;
+    float* xr = x + src * width;
+    constexpr int KEEP = 8;
+    float v[KEEP];
+    const float sg = (has_d && d.shared != nullptr && d.shared_gate != nullptr) ? d.shared_gate[src] : 1.f;
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < KEEP; ++i) {
+        const int e = threadIdx.x + i * blockDim.x;
+        v[i] = 0.f;
+        if (e < width) {
+            float dl = 0.f;
+            if (has_d) {
+                if (d.delta != nullptr) dl = d.delta[src * width + e];
+                if (d.pair_out != nullptr) {
+                    float ff = 0.f;
+                    for (int k = 0; k < d.top; ++k)
+                        ff = fmaf(d.sel_w[src * d.top + k], d.pair_out[(int64_t)d.pair_pos[src * d.top + k] * width + e], ff);
+                    dl += ff;
+                }
+                if (d.shared != nullptr) dl = fmaf(d.shared[src * width + e], sg, dl);
+                if (d.scale != nullptr) dl *= d.scale[e];
+                dl *= d.mult;
+            }
+            v[i] = xr[e] + dl;
+            sum += kind == UMBS_NORM_LAYER ? v[i] : v[i] * v[i];
+        }
+    }
+    float mean = 0.f, inv = 0.f;
+    if (y != nullptr) {
+        sum = block_sum_pn(sum, red);
+        if (kind == UMBS_NORM_LAYER) {
+            mean = sum / (float)width;
+            float dev = 0.f;
+#pragma unroll
+            for (int i = 0; i < KEEP; ++i)
+                if (threadIdx.x + i * blockDim.x < width) dev = fmaf(v[i] - mean, v[i] - mean, dev);
+            sum = block_sum_pn(dev, red);
+        }
+        inv = 1.f / sqrtf(sum / (float)width + eps);
+    }
+    const bool write_x = rows == nullptr && has_d;
+#pragma unroll
+    for (int i = 0; i < KEEP; ++i) {
+        const int e = threadIdx.x + i * blockDim.x;
+        if (e < width) {
+            if (write_x) xr[e] = v[i];
+            if (copy != nullptr) copy[(int64_t)r * width + e] = v[i];
+            if (y != nullptr) {
+                float o = (v[i] - mean) * inv * (w_offset + w[e]);
+                if (kind == UMBS_NORM_LAYER && bias != nullptr) o += bias[e];
+                y[(int64_t)r * width + e] = from_f32<T>(o);
+            }
+        }
+    }
+}
+
+// One block per token of a latent-attention layer with direct queries: RMS norm of the latent, the turn of the shared key
+// part and of every head's rope part by the token's position.
+template <typename T>
+__global__ void latent_prep_kernel(const float* __restrict__ proj, int64_t ld, Batch b, int heads, int dim, int rope, int R,
+                                   const float* __restrict__ kv_norm, float eps, int rot_dims, const float* __restrict__ inv_freq,
+                                   float rot_mag, T* __restrict__ q, T* __restrict__ c, float* __restrict__ q_rot, int64_t ld_qrot) {
+    extern __shared__ float cs[];                 // cos | sin [rot_dims]
+    __shared__ float red[33];
+    const int t = blockIdx.x, pos = b.tok_pos[t], half = rot_dims / 2, hd = dim + rope;
+    const float* row = proj + (int64_t)t * ld;
+    const float* low = row + (int64_t)heads * hd;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float ang = (float)pos * inv_freq[i];
+        cs[i] = cosf(ang) * rot_mag;
+        cs[half + i] = sinf(ang) * rot_mag;
+    }
+    float ss = 0.f;
+    for (int e = threadIdx.x; e < R; e += blockDim.x) ss = fmaf(low[e], low[e], ss);
+    ss = block_sum_pn(ss, red);                    // (its barriers also publish cs)
+    const float inv = 1.f / sqrtf(ss / (float)R + eps);
+    // the turn of component j of a rope part that starts at p
+    auto turned = [&](const float* p, int j) -> float {
+        if (j < half) return p[j] * cs[j] - p[j + half] * cs[half + j];
+        if (j < rot_dims) return p[j] * cs[j - half] + p[j - half] * cs[j];     // cs[j] = sin of pair j - half
+        return p[j];
+    };
+    T* crow = c + (int64_t)t * (R + rope);
+    for (int e = threadIdx.x; e < R; e += blockDim.x) crow[e] = from_f32<T>(low[e] * inv * kv_norm[e]);
+    for (int j = threadIdx.x; j < rope; j += blockDim.x) crow[R + j] = from_f32<T>(turned(low + R, j));
+    T* qrow = q + (int64_t)t * heads * hd;
+    for (int i = threadIdx.x; i < heads * hd; i += blockDim.x) {
+        const int h = i / hd, e = i - h * hd;
+        float o = row[i];
+        if (e >= dim) {
+            o = turned(row + (int64_t)h * hd + dim, e - dim);
+            if (q_rot != nullptr) q_rot[((int64_t)t * heads + h) * ld_qrot + (e - dim)] = o;
+        }
+        qrow[i] = from_f32<T>(o);
+    }
+}
+
 __global__ void softcap_kernel(float* __restrict__ z, int64_t n, float cap) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) z[i] = cap * tanhf(z[i] / cap);
@@ -196,6 +319,41 @@ extern "C" int umbs_add_rms_norm(int dtype, float* x, const float* delta, const 
     cudaStream_t st = (cudaStream_t)stream;
     const int threads = width >= 2048 ? 256 : (width >= 512 ? 128 : 64);
     UMBS_DISPATCH_T(dtype, add_rms_norm_kernel<T><<<n, threads, 0, st>>>(x, delta, rows, w, w_offset, width, eps, (T*)y, copy));
+    count_launches(1);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int umbs_add_norm(int dtype, float* x, const umbs_delta_t* d, const int32_t* rows, int n, int kind, const float* w,
+                             const float* b, float w_offset, int width, float eps, void* y, float* copy, umbs_stream_t stream) {
+    if (n <= 0) return 0;
+    if (x == nullptr || width <= 0 || (y != nullptr && w == nullptr)) return UMB_ERR_ARG;
+    if (kind != UMBS_NORM_RMS && kind != UMBS_NORM_LAYER) return UMB_ERR_ARG;
+    if (width > 8192) return UMB_ERR_UNSUPPORTED;                 // a row lives in the block's registers
+    if (d != nullptr && d->pair_out != nullptr && (d->sel_w == nullptr || d->pair_pos == nullptr || d->top < 1)) return UMB_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    int threads = ((width + 7) / 8 + 31) / 32 * 32;
+    if (threads < 64) threads = 64;
+    umbs_delta_t dd{};
+    if (d != nullptr) dd = *d;
+    UMBS_DISPATCH_T(dtype, add_norm_kernel<T><<<n, threads, 0, st>>>(x, dd, d != nullptr, rows, kind, w, b, w_offset, width, eps,
+                                                                     (T*)y, copy));
+    count_launches(1);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int umbs_latent_prep(int dtype, const float* proj, int64_t ld, const umbs_batch_t* batch, int heads, int dim,
+                                int rope_dim, int kv_rank, const float* kv_norm, float eps, int rot_dims, const float* inv_freq,
+                                float rot_mag, void* q, void* c, float* q_rot, int64_t ld_qrot, umbs_stream_t stream) {
+    if (batch->n_tokens <= 0) return 0;
+    if (heads < 1 || dim < 0 || rope_dim < 0 || kv_rank < 1 || rot_dims < 0 || rot_dims > rope_dim || (rot_dims & 1)) return UMB_ERR_ARG;
+    if (rot_dims > 0 && inv_freq == nullptr) return UMB_ERR_ARG;
+    if (proj == nullptr || kv_norm == nullptr || q == nullptr || c == nullptr) return UMB_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int work = heads * (dim + rope_dim);
+    const int threads = work >= 4096 ? 512 : (work >= 1024 ? 256 : 128);
+    UMBS_DISPATCH_T(dtype, latent_prep_kernel<T><<<batch->n_tokens, threads, (size_t)(rot_dims + 2) * sizeof(float), st>>>(
+                               proj, ld, *batch, heads, dim, rope_dim, kv_rank, kv_norm, eps, rot_dims, inv_freq, rot_mag, (T*)q,
+                               (T*)c, q_rot, ld_qrot));
     count_launches(1);
     return (int)cudaGetLastError();
 }

@@ -54,8 +54,13 @@ def _zedotar(path, **kw):
     return zedotar.from_pretrained(path, **kw)
 
 
+def _kulisun(path, **kw):
+    from . import kulisun
+    return kulisun.from_pretrained(path, **kw)
+
+
 # config.json ``architecture`` -> factory(path, device=, dtype=, max_length=, slots=, max_tokens=, ...)
-_ARCHITECTURES = {"Radanex": _radanex, "Zedotar": _zedotar}
+_ARCHITECTURES = {"Radanex": _radanex, "Zedotar": _zedotar, "Kulisun": _kulisun}
 
 
 def _make(model_name, offload=False, batch_size=1, max_length=None, device="cuda:0", dtype=torch.float16, **unused):

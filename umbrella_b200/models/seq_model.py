@@ -32,7 +32,13 @@ class SeqMlpSpec:
     limit: float = 0.0
     shared_ff: int = 0
     shared_limit: float = 0.0
-    act: str = "clamped_glu"          # or "gelu_tanh"
+    act: str = "clamped_glu"          # or "gelu_tanh", "silu"
+    route: str = "softmax_top"        # "softmax_top": the top logits, softmax over them | "sigmoid_groups": sigmoid
+                                      # scores, group-limited choice, chosen scores divided by their sum
+    groups: int = 1                   # sigmoid_groups: equal groups of neighbouring experts ...
+    keep: int = 1                     # ... of which the best `keep` (by the sum of their two largest scores) stay eligible
+    bias: bool = False                # the shared (dense) projections carry biases
+    shared_gate: bool = False         # the shared expert's output is multiplied by sigmoid(w . h), a number per token
 
 
 @dataclass
@@ -45,11 +51,14 @@ class SeqLayerSpec:
     rot_dims: int = 0
     rot_base: float = 10000.0
     decay: list = field(default_factory=list)
-    # latent attention
+    # latent attention (pre-norm form: q_rank 0 = queries straight from the layer input; also attn_mode, gate_kind 0 / 2,
+    # rot_dims <= rope_dim, inv_freq, rot_mag from below; window 0 = every earlier token)
     q_rank: int = 0
     kv_rank: int = 0
     window: int = 0
     scale: float = 1.0
+    rope_dim: int = 0                 # rotated query/key dimensions per head beside `dim`; the key's are shared by all heads
+    learned_sink: bool = False        # softmax_sink: the sink's score is a learned number per head instead of 0
     # cached attention (also: rot_dims, window (0 = every earlier token), scale)
     kv_heads: int = 0
     attn_mode: str = "softmax"        # "softmax" | "softmax_sink" | "sigmoid"
@@ -66,6 +75,9 @@ class SeqLayerSpec:
     # layer
     form: str = "parallel"
     norm_offset: float = 0.0          # added to the layer's norm weights (1: weights stored around zero)
+    norm_kind: str = "rms"            # pre-norm form: "rms" | "layer" (mean removed, weight and bias)
+    layer_scale: bool = False         # pre-norm form: every block's output is multiplied by a learned vector
+    residual_mult: float = 1.0        # pre-norm form: x += residual_mult * block output
     shift: bool = True
     depth_average: bool = True
     mlp: SeqMlpSpec | None = None
@@ -80,6 +92,8 @@ class SeqModelSpec:
     norm_eps: float = 1e-6
     norm_offset: float = 0.0          # added to the final norm's weight
     logit_softcap: float = 0.0        # > 0: logits <- cap tanh(logits / cap)
+    embed_scale: float = 1.0          # factor on the embedding rows
+    norm_kind: str = "rms"            # kind of the final norm (pre-norm form)
     eos_token_id: list = field(default_factory=list)
 
     # compatibility with the engines' view of a config
@@ -128,7 +142,9 @@ def rotary_inv_freq64(rot_dims: int, base: float) -> torch.Tensor:
 _MIXERS = {"retention": S.UMBS_MIX_RETENTION, "latent_attention": S.UMBS_MIX_LATENT_ATTENTION,
            "cached_attention": S.UMBS_MIX_CACHED_ATTENTION, "mlstm": S.UMBS_MIX_MLSTM}
 _ATTN_MODES = {"softmax": S.UMBS_ATTN_SOFTMAX, "softmax_sink": S.UMBS_ATTN_SOFTMAX_SINK, "sigmoid": S.UMBS_ATTN_SIGMOID}
-_ACTS = {"clamped_glu": S.UMBS_ACT_CLAMPED_GLU, "gelu_tanh": S.UMBS_ACT_GELU_TANH}
+_ACTS = {"clamped_glu": S.UMBS_ACT_CLAMPED_GLU, "gelu_tanh": S.UMBS_ACT_GELU_TANH, "silu": S.UMBS_ACT_SILU}
+_NORMS = {"rms": S.UMBS_NORM_RMS, "layer": S.UMBS_NORM_LAYER}
+_ROUTES = {"softmax_top": S.UMBS_ROUTE_SOFTMAX_TOP, "sigmoid_groups": S.UMBS_ROUTE_SIGMOID_GROUPS}
 
 
 class SeqStateModel:
@@ -188,8 +204,11 @@ class SeqStateModel:
     def _f32(self, t: torch.Tensor) -> torch.Tensor:
         return t.to(self.device, torch.float32).contiguous()
 
-    def load_head(self, embed: torch.Tensor, head: torch.Tensor, final_norm: torch.Tensor):
+    def load_head(self, embed: torch.Tensor, head: torch.Tensor, final_norm: torch.Tensor,
+                  final_norm_b: torch.Tensor | None = None):
         self.head_weights = dict(embed=self._act(embed), head=self._act(head), final_norm=self._f32(final_norm))
+        if self.spec.norm_kind == "layer":
+            self.head_weights["final_norm_b"] = self._f32(final_norm_b)
         self._c_model = None
 
     def load_layer(self, idx: int, w: dict):
@@ -202,14 +221,25 @@ class SeqStateModel:
             the keys), g [heads or heads vdim, width] (by gate_kind); q_b, k_b, v_b (biases); q_conv, k_conv [channels, taps];
             pb [heads] (score bias).
         mlstm: q, k [heads dim, width]; v, g [heads vdim, width]; i, f [heads, width] with i_b, f_b [heads]; out_norm [heads vdim].
-        pre-norm layers: norm2 [width] when they have a feed-forward.
-        feed-forward: router [experts, width]; experts: list of (gate, up, down); shared (or dense): (gate, up, down)."""
+        latent attention with direct queries (q_rank 0): q [heads (dim + rope_dim), width], dkv [kv_rank + rope_dim, width],
+            dkv_norm, uk, uv, g [heads vdim, width] (gate_kind 2), sink [heads] (learned_sink).
+        pre-norm layers: norm2 [width] when they have a feed-forward; norm_b, norm2_b (layer norm); ls1, ls2 [width] (layer scale).
+        feed-forward: router [experts, width]; experts: list of (gate, up, down); shared (or dense): (gate, up, down);
+            dense_b: (gate_b, up_b, down_b) with ``bias``; shared_gate [1, width] or [width]."""
         l = self.spec.layers[idx]
         d = dict(norm=self._f32(w["norm"]), o=self._act(w["o"]))
         if l.form == "prenorm":
             l.shift = l.depth_average = False
             if l.mlp is not None:
                 d["norm2"] = self._f32(w["norm2"])
+            if l.norm_kind == "layer":
+                d["norm_b"] = self._f32(w["norm_b"])
+                if l.mlp is not None:
+                    d["norm2_b"] = self._f32(w["norm2_b"])
+            if l.layer_scale:
+                d["ls1"] = self._f32(w["ls1"])
+                if l.mlp is not None:
+                    d["ls2"] = self._f32(w["ls2"])
         if l.shift:
             d["shift"] = self._f32(w["shift"])
         if l.depth_average:
@@ -221,6 +251,26 @@ class SeqStateModel:
                 torch.zeros(1, dtype=torch.float32, device=self.device)
             d["decay"] = torch.tensor([float(x) for x in l.decay], dtype=torch.float32, device=self.device)
             assert d["decay"].numel() == l.heads and d["w_in"].shape == (2 * l.heads * (l.dim + l.vdim), self.spec.width)
+        elif l.mixer == "latent_attention" and l.q_rank == 0:
+            if l.form != "prenorm":
+                raise ValueError("latent attention with direct queries is a pre-norm mixer")
+            hd1 = l.dim + l.rope_dim
+            d["w_in"] = self._act(torch.cat([w["q"], w["dkv"]] + ([w["g"]] if l.gate_kind else []), dim=0))
+            d["kv_norm"] = self._f32(w["dkv_norm"])
+            d["ukT"] = self._act(w["uk"].reshape(l.heads, l.dim, l.kv_rank).transpose(1, 2))
+            d["uv"] = self._act(w["uv"])
+            # fresh sequences: every head's unrotated keys, then its values, from one product over the latents
+            d["ukv"] = self._act(torch.cat([w["uk"], w["uv"]], dim=0))
+            if l.learned_sink:
+                d["sink"] = self._f32(w["sink"])
+            f = torch.tensor(l.inv_freq, dtype=torch.float64) if l.inv_freq is not None else \
+                rotary_inv_freq64(l.rot_dims, l.rot_base) if l.rot_dims else None
+            d["inv_freq"] = f.to(torch.float32).to(self.device) if l.rot_dims else \
+                torch.zeros(1, dtype=torch.float32, device=self.device)
+            assert w["q"].shape == (l.heads * hd1, self.spec.width) and w["dkv"].shape == (l.kv_rank + l.rope_dim, self.spec.width)
+            assert w["uk"].shape == (l.heads * l.dim, l.kv_rank) and d["uv"].shape == (l.heads * l.vdim, l.kv_rank)
+            assert l.gate_kind in (0, 2) and (not l.gate_kind or w["g"].shape[0] == l.heads * l.vdim)
+            assert l.rot_dims % 2 == 0 and l.rot_dims <= l.rope_dim and (not l.rot_dims or d["inv_freq"].numel() == l.rot_dims // 2)
         elif l.mixer == "latent_attention":
             d["w_in"] = self._act(torch.cat([w["dq"], w["dkv"]], dim=0))
             d["q_norm"], d["kv_norm"] = self._f32(w["dq_norm"]), self._f32(w["dkv_norm"])
@@ -271,6 +321,13 @@ class SeqStateModel:
                 g, u, dn = w["shared"] if "shared" in w else w["dense"]
                 d["s_gu"], d["s_down"] = self._act(torch.cat([g, u], dim=0)), self._act(dn)
                 assert d["s_gu"].shape == (2 * m.shared_ff, self.spec.width)
+                if m.bias:
+                    gb, ub, db = w["dense_b"]
+                    d["s_gu_b"], d["s_down_b"] = self._f32(torch.cat([gb, ub])), self._f32(db)
+                    assert d["s_gu_b"].numel() == 2 * m.shared_ff and d["s_down_b"].numel() == self.spec.width
+                if m.shared_gate:
+                    d["s_gate"] = self._f32(w["shared_gate"].reshape(-1))
+                    assert d["s_gate"].numel() == self.spec.width
         self.weights[idx] = d
         self._c_model = None
 
@@ -294,6 +351,8 @@ class SeqStateModel:
             cl.heads, cl.dim, cl.vdim = l.heads, l.dim, l.vdim
             cl.form = S.UMBS_FORM_PRENORM if l.form == "prenorm" else S.UMBS_FORM_PARALLEL
             cl.norm_offset, cl.norm2_w = l.norm_offset, p(w.get("norm2"))
+            cl.norm_kind, cl.norm_b, cl.norm2_b = _NORMS[l.norm_kind], p(w.get("norm_b")), p(w.get("norm2_b"))
+            cl.out_scale, cl.out_scale2, cl.residual_mult = p(w.get("ls1")), p(w.get("ls2")), l.residual_mult
             if l.mixer == "retention":
                 cl.rot_dims, cl.inv_freq, cl.decay = l.rot_dims, p(w["inv_freq"]), p(w["decay"])
                 cl.ret_state = p(cache.ret_state[i])
@@ -311,10 +370,13 @@ class SeqStateModel:
             else:
                 cl.q_rank, cl.kv_rank, cl.window, cl.ring_len = l.q_rank, l.kv_rank, l.window, cache.ring_len(l)
                 cl.scale = l.scale
-                cl.q_norm, cl.kv_norm, cl.w_uq, cl.w_ukT, cl.w_uv = p(w["q_norm"]), p(w["kv_norm"]), p(w["uq"]), \
+                cl.q_norm, cl.kv_norm, cl.w_uq, cl.w_ukT, cl.w_uv = p(w.get("q_norm")), p(w["kv_norm"]), p(w.get("uq")), \
                     p(w["ukT"]), p(w["uv"])
                 cl.w_ukv = p(w["ukv"]) if self.fresh_attention else None
                 cl.ring = p(cache.ring[i])
+                if l.q_rank == 0:
+                    cl.rope_dim, cl.rot_dims, cl.inv_freq, cl.rot_mag = l.rope_dim, l.rot_dims, p(w["inv_freq"]), l.rot_mag
+                    cl.attn_mode, cl.gate_kind, cl.sink = _ATTN_MODES[l.attn_mode], l.gate_kind, p(w.get("sink"))
             cl.w_in, cl.w_o, cl.norm_w = p(w["w_in"]), p(w["o"]), p(w["norm"])
             cl.shift_w, cl.shift_state = p(w.get("shift")), p(cache.shift[i])
             cl.depth_w = p(w.get("depth"))
@@ -326,12 +388,16 @@ class SeqStateModel:
                 cl.mlp.shared_ff, cl.mlp.shared_limit = m.shared_ff, m.shared_limit
                 cl.mlp.ws_gu, cl.mlp.ws_down = p(w.get("s_gu")), p(w.get("s_down"))
                 cl.mlp.act = _ACTS[m.act]
+                cl.mlp.route_mode, cl.mlp.groups, cl.mlp.keep = _ROUTES[m.route], m.groups, m.keep
+                cl.mlp.bias_gu, cl.mlp.bias_down = p(w.get("s_gu_b")), p(w.get("s_down_b"))
+                cl.mlp.w_shared_gate = p(w.get("s_gate"))
         m = S.Model()
         m.dtype = S.UMBS_BF16 if self.dtype == torch.bfloat16 else S.UMBS_F32
         m.width, m.vocab, m.n_layers, m.norm_groups, m.slots = sp.width, sp.vocab, self.num_layers, sp.norm_groups, cache.slots
         m.norm_eps, m.norm_offset, m.logit_softcap = sp.norm_eps, sp.norm_offset, sp.logit_softcap
         hw = self.head_weights
         m.embed, m.final_norm, m.head = p(hw["embed"]), p(hw["final_norm"]), p(hw["head"])
+        m.embed_scale, m.norm_kind, m.final_norm_b = sp.embed_scale, _NORMS[sp.norm_kind], p(hw.get("final_norm_b"))
         m.layers = C.cast(layers, C.POINTER(S.Layer))
         self._c_layers = layers
         self._c_model, self._c_version = m, self.cache.version
