@@ -286,6 +286,17 @@ int umbs_latent_prep(int dtype, const float* proj, int64_t ld, const umbs_batch_
                      int kv_rank, const float* kv_norm, float eps, int rot_dims, const float* inv_freq, float rot_mag, void* q,
                      void* c, float* q_rot, int64_t ld_qrot, umbs_stream_t stream);
 
+/* umbs_window_attention with options: k_shared (`dtype` [n_tokens, shared_dim], row stride ldks, or NULL) is a key part all
+ * heads share -- a head's key is its own dim numbers of k followed by it, and q holds dim + shared_dim numbers per head;
+ * window <= 0: every earlier token of the step; mode UMBS_ATTN_SOFTMAX_SINK: the denominator also holds exp(sink[head])
+ * (sink NULL: exp(0)); gate (fp32 [n_tokens, ldg] or NULL): the output is multiplied element by element by
+ * sigmoid(gate[t ldg + h vdim + c]).  dim + shared_dim <= 192, vdim <= 128 (umbs_window_attention_ex_fits). */
+int umbs_window_attention_ex_fits(int dim, int shared_dim, int vdim);
+int umbs_window_attention_ex(int dtype, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* k_shared,
+                             int64_t ldks, int shared_dim, const void* v, int64_t ldv, const umbs_batch_t* batch, int heads,
+                             int dim, int vdim, int window, float scale, int mode, const float* sink, const float* gate,
+                             int64_t ldg, void* out, int64_t ldo, umbs_stream_t stream);
+
 /* Stores this step's latents into the slots' rings (position p at row p mod ring_len). */
 int umbs_ring_append(int dtype, const void* c, void* ring, int ring_len, const umbs_batch_t* batch, int kv_rank,
                      umbs_stream_t stream);

@@ -176,3 +176,65 @@ def test_state_cache_of_cached_attention_and_mlstm_layers():
     capped = SequenceStateCache(spec, slots=1, device="cpu", dtype=torch.float32, max_length=30)
     with pytest.raises(RuntimeError):
         capped.reserve_length(31)
+
+
+# ---------------------------------------------------------------------------------------------- the Kulisun family
+def test_kulisun_config_reader_and_tensor_names():
+    import kul_helpers as U
+    from umbrella_b200.models.kulisun import layer_tensor_names, spec_from_config
+    spec = spec_from_config(U.config_json(U.MIXED))
+    assert (spec.width, spec.vocab, spec.norm_eps, spec.norm_kind, spec.embed_scale) == (64, 96, 1e-5, "layer", 3.0)
+    assert all(l.form == "prenorm" and l.mixer == "latent_attention" and l.q_rank == 0 and l.window == 0 and l.norm_kind == "layer"
+               and l.layer_scale and l.residual_mult == 0.6 and l.attn_mode == "softmax_sink" and l.learned_sink and l.gate_kind == 2
+               and not l.shift and not l.depth_average for l in spec.layers)
+    a, b, c, d, e = spec.layers[:5]
+    assert (a.heads, a.dim, a.rope_dim, a.vdim, a.kv_rank, a.scale, a.rot_dims) == (4, 16, 8, 24, 40, 0.2, 8)
+    assert (a.mlp.experts, a.mlp.shared_ff, a.mlp.act, a.mlp.bias, a.mlp.shared_gate) == (0, 48, "silu", True, False)
+    assert (b.mlp.experts, b.mlp.top, b.mlp.groups, b.mlp.keep, b.mlp.ff, b.mlp.shared_ff, b.mlp.route, b.mlp.shared_gate, b.mlp.bias) == \
+        (8, 3, 4, 2, 24, 32, "sigmoid_groups", True, False)
+    assert c.mlp is None and (c.rot_dims, c.rope_dim, c.rot_mag) == (4, 8, 1.0) and len(c.inv_freq) == 2
+    assert (d.rope_dim, d.rot_dims, d.inv_freq, d.mlp.shared_ff, d.mlp.groups, d.mlp.top) == (0, 0, None, 0, 1, 1)
+    assert e.rot_mag == pytest.approx(0.1 * __import__("math").log(8.0) + 1.0) and spec.layers[5].rot_dims == 0
+    names = set()
+    for i in range(len(spec.layers)):
+        for v in layer_tensor_names(spec, i).values():
+            names |= {v} if isinstance(v, str) else set(v) if isinstance(v, tuple) else {n for trio in v for n in trio}
+    assert names | {"embed", "head", "final.norm", "final.norm.b"} == set(U.random_tensors(U.MIXED))
+    bad = U.config_json(U.MIXED)
+    bad["layers"][1]["mlp"]["router"]["top"] = 5                      # two groups of two experts hold no five
+    with pytest.raises(ValueError):
+        spec_from_config(bad)
+    with pytest.raises(ValueError):
+        spec_from_config(dict(U.config_json(U.MIXED), architecture="Zedotar"))
+
+
+def test_kulisun_rotary_frequencies_match_the_plain_statement():
+    import kul_helpers as U
+    from oracle import kulisun as O
+    from umbrella_b200.models.kulisun import spec_from_config
+    spec = spec_from_config(U.config_json(U.MIXED))
+    for L, l in zip(U.MIXED["layers"], spec.layers):
+        if not l.rot_dims:
+            continue
+        f, mag = O.rotary_frequencies(U._rot(L))
+        assert torch.allclose(torch.tensor(l.inv_freq, dtype=torch.float64), torch.tensor(f, dtype=torch.float64), rtol=1e-12, atol=0)
+        assert abs(l.rot_mag - mag) < 1e-12
+
+
+def test_state_cache_of_windowless_latent_attention():
+    import kul_helpers as U
+    from umbrella_b200.attn.state_cache import SequenceStateCache
+    from umbrella_b200.models.kulisun import spec_from_config
+    spec = spec_from_config(U.config_json(U.MIXED))
+    c = SequenceStateCache(spec, slots=2, device="cpu", dtype=torch.float32, capacity=24)
+    assert c.ring[0].shape == (2, 24, 48) and c.ring[3].shape == (2, 24, 40) and c.ring[4].shape == (2, 24, 32)   # latent + shared part
+    assert c.shift[0] is None and c.kv_cache[0] is None
+    c.ring[0][1, 23].fill_(4.0)
+    v = c.version
+    c.reserve_length(24)
+    assert c.version == v
+    c.reserve_length(30)                                              # the rows double and keep their index
+    assert c.capacity == 48 and c.version > v and c.ring[0].shape == (2, 48, 48)
+    assert float(c.ring[0][1, 23].min()) == 4.0 and float(c.ring[0][1, 24:].abs().max()) == 0
+    s = [c.alloc_slot() for _ in range(3)]
+    assert c.slots == 4 and c.ring[0].shape == (4, 48, 48) and float(c.ring[0][1, 23].min()) == 4.0

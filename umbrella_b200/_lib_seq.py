@@ -95,6 +95,10 @@ SIGNATURES = {
     "umbs_window_attention_fits": (c_int, [c_int, c_int]),
     "umbs_window_attention": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, _BP, c_int, c_int,
                                       c_int, c_int, c_float, c_void_p, c_int64, c_void_p]),
+    "umbs_window_attention_ex_fits": (c_int, [c_int, c_int, c_int]),
+    "umbs_window_attention_ex": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p,
+                                         c_int64, _BP, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
+                                         c_int64, c_void_p, c_int64, c_void_p]),
     "umbs_ring_append": (c_int, [c_int, c_void_p, c_void_p, c_int, _BP, c_int, c_void_p]),
     "umbs_moe_route": (c_int, [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_void_p, c_void_p]),

@@ -211,16 +211,29 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
             UMBS_TRY(umbs_gemm(dt, s.h, W, 0, l.w_in, W, 0, s.proj, rows, 0, 1, T, rows, W, 1, nullptr, nullptr, 0, 0.f, stream));
             UMBS_TRY(umbs_latent_prep(dt, s.proj, rows, b, l.heads, l.dim, Rt, R, l.kv_norm, m->norm_eps, l.rot_dims, l.inv_freq,
                                       l.rot_mag, s.q, s.c, s.q_abs + R, KD, stream));
-            // q_abs[t, h, :R] = W_uk[h]^T q[t, h, :dim]: scores against the cached latents need no per-key up-projection;
-            // q_abs[t, h, R:] is the head's rotated part, written by the kernel above
-            UMBS_TRY(umbs_gemm(dt, s.q, hdq, hd1, l.w_ukT, l.dim, (int64_t)R * l.dim, s.q_abs, (int64_t)l.heads * KD, KD, 1, T, R,
-                               l.dim, l.heads, nullptr, nullptr, 0, 0.f, stream));
-            UMBS_TRY(umbs_latent_attention_ex(dt, s.q_abs, s.c, l.ring, l.ring_len, b, l.heads, R, Rt, l.window, l.scale,
-                                              l.attn_mode, l.sink, s.la_part, s.la_part_bytes, s.o_lat, stream));
-            UMBS_TRY(umbs_ring_append(dt, s.c, l.ring, l.ring_len, b, KD, stream));
-            // values per head from the weighted latents, times the sigmoid output gate
-            UMBS_TRY(umbs_gemm_ex(dt, s.o_lat, (int64_t)l.heads * R, R, l.w_uv, R, (int64_t)l.vdim * R, s.mixed, hv, l.vdim, 0, T,
-                                  l.vdim, R, l.heads, nullptr, nullptr, 0, 0.f, nullptr, gate, rows, l.vdim, stream));
+            if (b->max_seq_len > 1 && b->max_pos0 == 0 && l.w_ukv != nullptr && umbs_window_attention_ex_fits(l.dim, Rt, l.vdim)) {
+                // a step of fresh sequences: every visible key is in the step, so every head's own key part and its values
+                // are up-projected once per token and a (row, key) pair costs dim + rope_dim + vdim multiply-adds
+                const int hdk = l.heads * l.dim;
+                const size_t es = dt == UMBS_F32 ? 4 : 2;
+                UMBS_TRY(umbs_gemm(dt, s.c, KD, 0, l.w_ukv, R, 0, s.kv, hdk + hv, 0, 0, T, hdk + hv, R, 1, nullptr, nullptr, 0, 0.f,
+                                   stream));
+                UMBS_TRY(umbs_window_attention_ex(dt, s.q, hdq, s.kv, hdk + hv, (const char*)s.c + (size_t)R * es, KD, Rt,
+                                                  (const char*)s.kv + (size_t)hdk * es, hdk + hv, b, l.heads, l.dim, l.vdim,
+                                                  l.window, l.scale, l.attn_mode, l.sink, gate, rows, s.mixed, hv, stream));
+                UMBS_TRY(umbs_ring_append(dt, s.c, l.ring, l.ring_len, b, KD, stream));
+            } else {
+                // q_abs[t, h, :R] = W_uk[h]^T q[t, h, :dim]: scores against the cached latents need no per-key up-projection;
+                // q_abs[t, h, R:] is the head's rotated part, written by the kernel above
+                UMBS_TRY(umbs_gemm(dt, s.q, hdq, hd1, l.w_ukT, l.dim, (int64_t)R * l.dim, s.q_abs, (int64_t)l.heads * KD, KD, 1, T,
+                                   R, l.dim, l.heads, nullptr, nullptr, 0, 0.f, stream));
+                UMBS_TRY(umbs_latent_attention_ex(dt, s.q_abs, s.c, l.ring, l.ring_len, b, l.heads, R, Rt, l.window, l.scale,
+                                                  l.attn_mode, l.sink, s.la_part, s.la_part_bytes, s.o_lat, stream));
+                UMBS_TRY(umbs_ring_append(dt, s.c, l.ring, l.ring_len, b, KD, stream));
+                // values per head from the weighted latents, times the sigmoid output gate
+                UMBS_TRY(umbs_gemm_ex(dt, s.o_lat, (int64_t)l.heads * R, R, l.w_uv, R, (int64_t)l.vdim * R, s.mixed, hv, l.vdim, 0,
+                                      T, l.vdim, R, l.heads, nullptr, nullptr, 0, 0.f, nullptr, gate, rows, l.vdim, stream));
+            }
         } else {
             return UMB_ERR_UNSUPPORTED;
         }

@@ -20,12 +20,24 @@ namespace umbs {
 
 constexpr int kWaQ = 64, kWaK = 64, kWaS = 68;        // rows and keys per tile; row stride of the [d][row] tiles
 
+// Options beside the plain form: a key part all heads share (ks: [n_tokens, sdim] with row stride ldks; a head's key is its
+// own dim numbers followed by the shared sdim, its query has dim + sdim numbers; here `dim` is that sum and `kdim` the head's
+// own part), a sink (a score without key or value that counts once in the sum: sink[h], or 0 without the array) and a
+// sigmoid gate per output element.
+struct WindowExtra {
+    const void* ks; int64_t ldks; int kdim;
+    int use_sink; const float* sink;
+    const float* gate; int64_t ldg;
+};
+
 template <typename T, int VC>
 __global__ void __launch_bounds__(256) window_attention_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k,
                                                                int64_t ldk, const T* __restrict__ v, int64_t ldv, Batch b,
                                                                int dim, int vdim, int window, float scale,
-                                                               T* __restrict__ out, int64_t ldo) {
+                                                               T* __restrict__ out, int64_t ldo, WindowExtra x) {
     extern __shared__ __align__(16) float sm[];
+    const T* ks = (const T*)x.ks;
+    const int kdim = x.kdim;
     constexpr int VW = 16 * VC, VP = VW + 4;          // value columns a block covers; row stride of the value tile
     float* Qs = sm;                                   // [dim][kWaS]  Qs[d][row]
     float* Ks = Qs + (size_t)dim * kWaS;              // [dim][kWaS]  Ks[d][key]
@@ -42,8 +54,8 @@ __global__ void __launch_bounds__(256) window_attention_kernel(const T* __restri
     float m[4], l[4], o[4][VC];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        m[i] = -INFINITY;
-        l[i] = 0.f;
+        m[i] = x.use_sink ? (x.sink ? x.sink[h] : 0.f) : -INFINITY;
+        l[i] = x.use_sink ? 1.f : 0.f;
 #pragma unroll
         for (int c = 0; c < VC; ++c) o[i][c] = 0.f;
     }
@@ -52,7 +64,11 @@ __global__ void __launch_bounds__(256) window_attention_kernel(const T* __restri
         __syncthreads();                              // the previous tile is consumed (first time round: Qs is written)
         for (int i = tid; i < kWaK * dim; i += 256) {
             const int kk = i / dim, d = i - kk * dim, j = j0 + kk;
-            Ks[d * kWaS + kk] = j <= row_hi ? to_f32(k[(int64_t)(start + j) * ldk + (int64_t)h * dim + d]) : 0.f;
+            float kvl = 0.f;
+            if (j <= row_hi)
+                kvl = d < kdim ? to_f32(k[(int64_t)(start + j) * ldk + (int64_t)h * kdim + d])
+                               : to_f32(ks[(int64_t)(start + j) * x.ldks + (d - kdim)]);
+            Ks[d * kWaS + kk] = kvl;
         }
         for (int i = tid; i < kWaK * VW; i += 256) {
             const int kk = i / VW, c = i - kk * VW, j = j0 + kk;
@@ -126,12 +142,17 @@ __global__ void __launch_bounds__(256) window_attention_kernel(const T* __restri
         if (r >= len) continue;
         const float inv = 1.f / l[i];
         T* orow = out + (int64_t)(start + r) * ldo + (int64_t)h * vdim;
+        const float* grow = x.gate ? x.gate + (int64_t)(start + r) * x.ldg + (int64_t)h * vdim : nullptr;
 #pragma unroll
         for (int cb = 0; cb < VC / 4; ++cb)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int col = cb * 64 + tx * 4 + c;
-                if (col < vdim) orow[col] = from_f32<T>(o[i][cb * 4 + c] * inv);
+                if (col < vdim) {
+                    float val = o[i][cb * 4 + c] * inv;
+                    if (grow != nullptr) val *= 1.f / (1.f + expf(-grow[col]));
+                    orow[col] = from_f32<T>(val);
+                }
             }
     }
 }
@@ -139,7 +160,7 @@ __global__ void __launch_bounds__(256) window_attention_kernel(const T* __restri
 template <typename T, int VC>
 static int launch_window_attention(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
                                    const Batch& b, int heads, int dim, int vdim, int window, float scale, void* out,
-                                   int64_t ldo, cudaStream_t st) {
+                                   int64_t ldo, const WindowExtra& x, cudaStream_t st) {
     const size_t smem = ((size_t)2 * dim * kWaS + (size_t)kWaK * (16 * VC + 4) + (size_t)kWaK * kWaS) * sizeof(float);
     static size_t set = 0;
     if (smem > 48 * 1024 && smem > set) {
@@ -150,7 +171,7 @@ static int launch_window_attention(const void* q, int64_t ldq, const void* k, in
     }
     const dim3 grid((b.max_seq_len + kWaQ - 1) / kWaQ, heads, b.n_seqs);
     window_attention_kernel<T, VC><<<grid, 256, smem, st>>>((const T*)q, ldq, (const T*)k, ldk, (const T*)v, ldv, b, dim, vdim,
-                                                            window, scale, (T*)out, ldo);
+                                                            window, scale, (T*)out, ldo, x);
     return 0;
 }
 
@@ -159,21 +180,38 @@ static int launch_window_attention(const void* q, int64_t ldq, const void* k, in
 using namespace umbs;
 
 extern "C" int umbs_window_attention_fits(int dim, int vdim) { return dim >= 1 && dim <= 128 && vdim >= 1 && vdim <= 128; }
+extern "C" int umbs_window_attention_ex_fits(int dim, int shared_dim, int vdim) {
+    return dim >= 1 && shared_dim >= 0 && dim + shared_dim <= 192 && vdim >= 1 && vdim <= 128;
+}
 
 extern "C" int umbs_window_attention(int dtype, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
                                      int64_t ldv, const umbs_batch_t* batch, int heads, int dim, int vdim, int window,
                                      float scale, void* out, int64_t ldo, umbs_stream_t stream) {
-    if (batch->n_tokens <= 0) return 0;
-    if (window < 1 || heads < 1) return UMB_ERR_ARG;
+    if (window < 1) return UMB_ERR_ARG;
     if (!umbs_window_attention_fits(dim, vdim)) return UMB_ERR_UNSUPPORTED;
+    return umbs_window_attention_ex(dtype, q, ldq, k, ldk, nullptr, 0, 0, v, ldv, batch, heads, dim, vdim, window, scale,
+                                    UMBS_ATTN_SOFTMAX, nullptr, nullptr, 0, out, ldo, stream);
+}
+
+extern "C" int umbs_window_attention_ex(int dtype, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* k_shared,
+                                        int64_t ldks, int shared_dim, const void* v, int64_t ldv, const umbs_batch_t* batch,
+                                        int heads, int dim, int vdim, int window, float scale, int mode, const float* sink,
+                                        const float* gate, int64_t ldg, void* out, int64_t ldo, umbs_stream_t stream) {
+    if (batch->n_tokens <= 0) return 0;
+    if (heads < 1 || (shared_dim > 0 && k_shared == nullptr)) return UMB_ERR_ARG;
+    if (mode != UMBS_ATTN_SOFTMAX && mode != UMBS_ATTN_SOFTMAX_SINK) return UMB_ERR_UNSUPPORTED;
+    if (!umbs_window_attention_ex_fits(dim, shared_dim, vdim)) return UMB_ERR_UNSUPPORTED;
+    if (window <= 0) window = 1 << 30;                       // every earlier token of the step
     cudaStream_t st = (cudaStream_t)stream;
+    const WindowExtra x{k_shared, ldks, dim, mode == UMBS_ATTN_SOFTMAX_SINK, sink, gate, ldg};
+    const int dq = dim + shared_dim;
     int rc;
     if (dtype == UMBS_BF16) {
-        rc = vdim <= 64 ? launch_window_attention<__nv_bfloat16, 4>(q, ldq, k, ldk, v, ldv, *batch, heads, dim, vdim, window, scale, out, ldo, st)
-                        : launch_window_attention<__nv_bfloat16, 8>(q, ldq, k, ldk, v, ldv, *batch, heads, dim, vdim, window, scale, out, ldo, st);
+        rc = vdim <= 64 ? launch_window_attention<__nv_bfloat16, 4>(q, ldq, k, ldk, v, ldv, *batch, heads, dq, vdim, window, scale, out, ldo, x, st)
+                        : launch_window_attention<__nv_bfloat16, 8>(q, ldq, k, ldk, v, ldv, *batch, heads, dq, vdim, window, scale, out, ldo, x, st);
     } else if (dtype == UMBS_F32) {
-        rc = vdim <= 64 ? launch_window_attention<float, 4>(q, ldq, k, ldk, v, ldv, *batch, heads, dim, vdim, window, scale, out, ldo, st)
-                        : launch_window_attention<float, 8>(q, ldq, k, ldk, v, ldv, *batch, heads, dim, vdim, window, scale, out, ldo, st);
+        rc = vdim <= 64 ? launch_window_attention<float, 4>(q, ldq, k, ldk, v, ldv, *batch, heads, dq, vdim, window, scale, out, ldo, x, st)
+                        : launch_window_attention<float, 8>(q, ldq, k, ldk, v, ldv, *batch, heads, dq, vdim, window, scale, out, ldo, x, st);
     } else {
         return UMB_ERR_ARG;
     }

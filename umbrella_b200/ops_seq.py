@@ -226,3 +226,122 @@ def mlstm(proj, gate_bias, batch: RaggedBatch, heads, dim, vdim, gate_cap, eps, 
                                 float(gate_cap), float(eps), _p(out_norm_w), _p(state), _p(gates), _p(o32), _p(seg),
                                 seg.numel() * 4 if seg is not None else 0, _p(out), _stream()), "mlstm")
     return out
+
+
+# ---------------------------------------------------------------------------------------------- further options of the pre-norm form
+def gemm_ex(a: torch.Tensor, w: torch.Tensor, *, out_f32: bool = False, groups: int = 1, a_goff: int = 0, c_goff: int = 0,
+            n: int | None = None, k: int | None = None, act: int = 0, limit: float = 0.0, bias=None, out_gate=None,
+            gate_goff: int = 0) -> torch.Tensor:
+    """``gemm`` with the epilogue of umbs_gemm_ex: ``act`` = 0 (plain) or UMBS_ACT_* over gate|up rows, ``bias`` fp32 [N] or
+    [2 N], ``out_gate`` fp32 [M, .] whose sigmoid multiplies the result (column g gate_goff + n for group g)."""
+    mode = _mode(a)
+    assert w.dtype == a.dtype and a.stride(-1) == 1 and w.is_contiguous()
+    w3 = w if w.dim() == 3 else w.unsqueeze(0)
+    K = w3.shape[2] if k is None else k
+    N = (w3.shape[1] // (2 if act else 1)) if n is None else n
+    M = a.shape[0]
+    out = torch.zeros((M, N if groups == 1 else groups * c_goff), dtype=torch.float32 if out_f32 else a.dtype, device=a.device)
+    S.check(S.load().umbs_gemm_ex(mode, _p(a), a.stride(0), a_goff, _p(w3), w3.stride(1), w3.stride(0), _p(out), out.stride(0),
+                                  c_goff, int(out_f32), M, N, K, groups, None, None, int(act), float(limit), _p(bias),
+                                  _p(out_gate), out_gate.stride(0) if out_gate is not None else 0, gate_goff, _stream()),
+            "gemm_ex")
+    return out
+
+
+def add_norm(x, w, b, eps: float, kind: int = S.UMBS_NORM_LAYER, w_offset: float = 0.0, dtype=torch.float32, rows=None,
+             delta=None, pair_out=None, sel_w=None, pair_pos=None, shared=None, shared_gate=None, scale=None, mult: float = 1.0,
+             want_copy: bool = False):
+    """x [n, width] fp32 += (delta + routed pairs + gated shared) * scale * mult (in place when ``rows`` is None), then the
+    norm of the sum as ``dtype`` (and a copy of the sum)."""
+    n = x.shape[0] if rows is None else rows.numel()
+    y = torch.empty((n, x.shape[1]), dtype=dtype, device=x.device)
+    copy = torch.empty((n, x.shape[1]), dtype=torch.float32, device=x.device) if want_copy else None
+    d = None
+    if any(t is not None for t in (delta, pair_out, shared)):
+        d = S.Delta()
+        d.delta, d.pair_out, d.sel_w, d.pair_pos = (t.data_ptr() if t is not None else None for t in (delta, pair_out, sel_w, pair_pos))
+        d.top = sel_w.shape[1] if sel_w is not None else 0
+        d.shared, d.shared_gate, d.scale = (t.data_ptr() if t is not None else None for t in (shared, shared_gate, scale))
+        d.mult = float(mult)
+    S.check(S.load().umbs_add_norm(_mode(y), _p(x), C.byref(d) if d is not None else None, _p(rows), n, kind, _p(w), _p(b),
+                                   float(w_offset), x.shape[1], float(eps), _p(y), _p(copy), _stream()), "add_norm")
+    return (y, copy) if want_copy else y
+
+
+def latent_prep(proj, batch: RaggedBatch, heads, dim, rope_dim, kv_rank, kv_norm, eps, rot_dims, inv_freq, rot_mag=1.0,
+                dtype=torch.float32):
+    """proj fp32 [T, q | latent | shared key part | ...] -> (q [T, heads (dim + rope_dim)], c [T, kv_rank + rope_dim]) as
+    ``dtype`` and q_abs fp32 [T, heads, kv_rank + rope_dim] whose last rope_dim columns hold every head's turned part (the
+    first kv_rank are left for the product with the key up-projection)."""
+    T = proj.shape[0]
+    KD = kv_rank + rope_dim
+    q = torch.empty((T, heads * (dim + rope_dim)), dtype=dtype, device=proj.device)
+    c = torch.empty((T, KD), dtype=dtype, device=proj.device)
+    q_abs = torch.zeros((T, heads, KD), dtype=torch.float32, device=proj.device)
+    S.check(S.load().umbs_latent_prep(_mode(q), _p(proj), proj.stride(0), C.byref(batch.c), heads, dim, rope_dim, kv_rank,
+                                      _p(kv_norm), float(eps), rot_dims, _p(inv_freq), float(rot_mag), _p(q), _p(c),
+                                      C.c_void_p(q_abs.data_ptr() + 4 * kv_rank), KD, _stream()), "latent_prep")
+    return q, c, q_abs
+
+
+def latent_attention_shared(q_abs, c, ring, batch: RaggedBatch, heads, kv_rank, rope_dim, scale, window: int = 0,
+                            sink=None, use_sink: bool = True, append: bool = True, split: bool = True):
+    """Attention over [latent | shared part] keys (umbs_latent_attention_ex) -> [T, heads kv_rank]; appends the step's rows."""
+    T = c.shape[0]
+    out = torch.empty((T, heads * kv_rank), dtype=c.dtype, device=c.device)
+    lib = S.load()
+    part = torch.empty(512 * heads * (kv_rank + 2), dtype=torch.float32, device=c.device) if split and T <= 64 else None
+    S.check(lib.umbs_latent_attention_ex(_mode(c), _p(q_abs), _p(c), _p(ring), ring.shape[1], C.byref(batch.c), heads, kv_rank,
+                                         rope_dim, window, float(scale),
+                                         S.UMBS_ATTN_SOFTMAX_SINK if use_sink else S.UMBS_ATTN_SOFTMAX, _p(sink), _p(part),
+                                         part.numel() * 4 if part is not None else 0, _p(out), _stream()), "latent_attention_ex")
+    if append:
+        S.check(lib.umbs_ring_append(_mode(c), _p(c), _p(ring), ring.shape[1], C.byref(batch.c), kv_rank + rope_dim, _stream()),
+                "ring_append")
+    return out
+
+
+def window_attention_shared(q, k, k_shared, v, batch: RaggedBatch, heads: int, scale: float, window: int = 0, sink=None,
+                            use_sink: bool = True, gate=None):
+    """q [T, heads (dim + shared)], k [T, heads dim], k_shared [T, shared], v [T, heads vdim] (row-strided views are fine)
+    -> [T, heads vdim]: attention among the step's own tokens with a key part all heads share, a sink and an output gate."""
+    T = q.shape[0]
+    sd = k_shared.shape[1] if k_shared is not None else 0
+    dim, vdim = k.shape[1] // heads, v.shape[1] // heads
+    assert q.shape[1] == heads * (dim + sd)
+    out = torch.empty((T, heads * vdim), dtype=q.dtype, device=q.device)
+    S.check(S.load().umbs_window_attention_ex(_mode(q), _p(q), q.stride(0), _p(k), k.stride(0), _p(k_shared),
+                                              k_shared.stride(0) if k_shared is not None else 0, sd, _p(v), v.stride(0),
+                                              C.byref(batch.c), heads, dim, vdim, window, float(scale),
+                                              S.UMBS_ATTN_SOFTMAX_SINK if use_sink else S.UMBS_ATTN_SOFTMAX, _p(sink), _p(gate),
+                                              gate.stride(0) if gate is not None else 0, _p(out), heads * vdim, _stream()),
+            "window_attention_ex")
+    return out
+
+
+def moe_route_ex(h, w_router, top: int, mode: int, groups: int = 1, keep: int = 1):
+    """``moe_route`` with the rule as an argument (UMBS_ROUTE_*)."""
+    n, width = h.shape
+    E = w_router.shape[0]
+    dev = h.device
+    sel_w = torch.empty((n, top), dtype=torch.float32, device=dev)
+    grp_off = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    pair_tok = torch.empty(n * top, dtype=torch.int32, device=dev)
+    pair_pos = torch.empty(n * top, dtype=torch.int32, device=dev)
+    scratch = torch.empty(2 * E + n * top, dtype=torch.int32, device=dev)
+    S.check(S.load().umbs_moe_route_ex(_mode(h), _p(h), n, width, _p(w_router), E, top, mode, groups, keep, _p(sel_w),
+                                       _p(grp_off), _p(pair_tok), _p(pair_pos), _p(scratch), _stream()), "moe_route_ex")
+    return sel_w, grp_off, pair_tok, pair_pos, scratch[2 * E:].view(n, top)
+
+
+def token_gate(h, w):
+    g = torch.empty(h.shape[0], dtype=torch.float32, device=h.device)
+    S.check(S.load().umbs_token_gate(_mode(h), _p(h), h.shape[0], h.shape[1], _p(w), _p(g), _stream()), "token_gate")
+    return g
+
+
+def embedding_scaled(ids, table, scale: float):
+    y = torch.empty((ids.numel(), table.shape[1]), dtype=torch.float32, device=table.device)
+    S.check(S.load().umbs_embedding_scaled(_mode(table), _p(ids), _p(table), float(scale), _p(y), ids.numel(), table.shape[1],
+                                           _stream()), "embedding_scaled")
+    return y

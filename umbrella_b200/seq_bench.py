@@ -436,3 +436,194 @@ def run_zedotar(args):
                        "l2": "whole-model runs stream more than L2 per step; kernel table flushes L2 between runs"},
             "sizes": sizes, "kernels": table}
     print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------- the Kulisun family
+def kulisun_config(width: int, layers: int = 8) -> dict:
+    """A Kulisun config with the layer sizes of a model of this width: latent attention in every layer (a latent of a
+    quarter of the width plus 64 rotated dimensions per cached token, heads of 128 + 64 and values of 128), the first
+    layer's feed-forward dense, the others routed with the active width Radanex has (2 of 16 experts in 4 groups of which
+    2 stay eligible, plus a shared expert)."""
+    heads = width // 128
+    mixer = dict(heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=width // 4, scale=192 ** -0.5,
+                 rot=dict(dims=64, base=1e4, scaling=dict(factor=40.0, original=4096, fast=32.0, slow=1.0)))
+    moe = dict(kind="moe", router=dict(experts=16, top=2, groups=dict(count=4, keep=2)), expert=dict(ff=width // 2),
+               shared=dict(ff=width))
+    return dict(architecture="Kulisun", width=width, vocab=32768, norm=dict(eps=1e-5), embedding=dict(scale=width ** 0.5),
+                residual_mult=0.7,
+                layers=[dict(type="latent_attention", mixer=mixer, mlp=dict(kind="dense", ff=2 * width) if i == 0 else moe)
+                        for i in range(layers)])
+
+
+def bench_kulisun(width, layers, device, prompt, ctx, batches, timer):
+    from .models.kulisun import Kulisun, spec_from_config
+    spec = spec_from_config(kulisun_config(width, layers))
+    m = Kulisun(spec, device=device, dtype=torch.bfloat16, slots=max(batches), max_tokens=prompt + ctx)
+    return bench_seq_model(m, spec, prompt, ctx, batches, timer)
+
+
+def kernel_table_kulisun(km, rm, device, timer, T=4096):
+    """Device time of each Kulisun mechanism at prefill size (one sequence of T tokens) and at decode size (8 sequences behind
+    512 tokens), with its roofline fractions, and the like kernel of the Radanex path measured the same way in the same
+    run (``like`` names the pairing)."""
+    from . import _lib_seq as S, ops_seq as Q
+    hbm, tflops, how = _peaks()
+    sp, W = km.spec, km.spec.width
+    fp32_peak = 148 * 128 * 2 * 1.965e-3
+    rows = []
+
+    def add(name, ms, nbytes=0, flops=0, like=None, flops32=0):
+        r = dict(kernel=name, ms=round(ms, 4))
+        if flops32:
+            r["fp32_tflops"], r["frac_of_fp32_fma_peak"] = round(flops32 / ms / 1e9, 2), round(flops32 / ms / 1e9 / fp32_peak, 3)
+        if flops:
+            r["tflops"], r["frac_of_bf16_peak"] = round(flops / ms / 1e9, 1), round(flops / ms / 1e9 / tflops, 3)
+        if nbytes:
+            r["gb_s"], r["frac_of_hbm_peak"] = round(nbytes / ms / 1e6, 1), round(nbytes / ms / 1e6 / hbm, 3)
+        if like:
+            r["like"] = like
+        rows.append(r)
+    l = sp.layers[1]
+    dw, mw = km.weights[0], km.weights[1]
+    rsp = rm.spec
+    ret = next(x for x in rsp.layers if x.mixer == "retention")
+    lat = next(x for x in rsp.layers if x.mixer == "latent_attention")
+    rw, lw = rm.weights[rsp.layers.index(ret)], rm.weights[rsp.layers.index(lat)]
+    bf = dict(dtype=torch.bfloat16, device=device)
+    ctx = 512
+    km.cache.reserve_length(T)
+    H, D, Rt, V, R = l.heads, l.dim, l.rope_dim, l.vdim, l.kv_rank
+    KD = R + Rt
+    for n, tag in ((T, f"prefill T={T}"), (8, "decode T=8")):
+        nseq = 1 if n == T else 8
+        per = n // nseq
+        pos0 = 0 if n == T else ctx
+        batch = Q.RaggedBatch([(s, per, pos0, 0) for s in range(nseq)], device)
+        x, d = torch.randn(n, W, device=device), torch.randn(n, W, device=device)
+        h = torch.randn(n, W, **bf)
+        # residual + norm: dense pending output, and the routed + shared sums
+        ms = timer(lambda: Q.add_norm(x, dw["norm"], dw["norm_b"], sp.norm_eps, dtype=torch.bfloat16, delta=d, scale=dw["ls1"], mult=0.7))
+        add(f"residual add (layer scale, multiplier) + layer norm ({tag})", ms, nbytes=n * W * (4 + 4 + 4 + 2), like="group norm + token shift")
+        f = l.mlp
+        sel_w, grp_off, pair_tok, pair_pos, _ = Q.moe_route_ex(h, mw["router"], f.top, S.UMBS_ROUTE_SIGMOID_GROUPS, f.groups, f.keep)
+        pair_out, sg = torch.randn(n * f.top, W, device=device), torch.rand(n, device=device)
+        ms = timer(lambda: Q.add_norm(x, dw["norm"], dw["norm_b"], sp.norm_eps, dtype=torch.bfloat16, pair_out=pair_out, sel_w=sel_w,
+                                      pair_pos=pair_pos, shared=d, shared_gate=sg, scale=dw["ls1"], mult=0.7))
+        add(f"residual add of {f.top} routed + gated shared outputs + layer norm ({tag})", ms, nbytes=n * W * (4 + 4 + 4 + 2 + 4 * f.top),
+            like="residual + depth average")
+        st = rm.cache.shift[rsp.layers.index(ret)]
+        ms = timer(lambda: Q.group_norm_shift(x, rw["norm"], rw["shift"], st, batch, rsp.norm_groups, rsp.norm_eps, torch.bfloat16))
+        add(f"radanex group norm + token shift ({tag})", ms, nbytes=n * W * (4 + 2 + 2))
+        stack, dwt = torch.randn(len(rsp.layers) + 1, n, W, device=device), rm.weights[-1]["depth"]
+        rpo = torch.randn(n * ret.mlp.top, W, device=device)
+        rsel, _, _, rpp, _ = Q.moe_route(h, rw["router"], ret.mlp.top)
+        ms = timer(lambda: Q.depth_mix(x, d, stack, len(rsp.layers) - 1, dwt, pair_out=rpo, sel_w=rsel, pair_pos=rpp, shared=d))
+        add(f"radanex residual of routed + shared outputs + depth average over {len(rsp.layers) + 1} streams ({tag})", ms,
+            nbytes=n * W * 4 * (len(rsp.layers) + 5 + ret.mlp.top))
+        # feed-forward products
+        gu = dw["s_gu"]
+        ms = timer(lambda: Q.gemm_ex(h, gu, act=S.UMBS_ACT_SILU, bias=dw["s_gu_b"]))
+        add(f"gemm dense gate|up + bias + silu [{n} x {W}] x [{gu.shape[0]} x {W}] ({tag})", ms,
+            nbytes=gu.numel() * 2 + n * W * 2 + n * gu.shape[0], flops=2 * n * W * gu.shape[0], like="gemm shared gate|up")
+        rgu = rw["s_gu"]
+        ms = timer(lambda: Q.gemm(h, rgu, dual=True, limit=7.0))
+        add(f"radanex gemm shared gate|up + clamped glu [{n} x {W}] x [{rgu.shape[0]} x {W}] ({tag})", ms,
+            nbytes=rgu.numel() * 2 + n * W * 2 + n * rgu.shape[0], flops=2 * n * W * rgu.shape[0])
+        ms = timer(lambda: Q.gemm(h, mw["gu"], groups=f.experts, n=f.ff, dual=S.UMBS_ACT_SILU, grp_off=grp_off, row_src=pair_tok,
+                                  rows=n * f.top, max_rows=n))
+        touched = min(f.experts, n * f.top)
+        add(f"gemm routed gate|up + silu, {f.experts} experts top {f.top} ({tag})", ms,
+            nbytes=touched * 2 * f.ff * W * 2 + n * W * 2 + n * f.top * f.ff * 2, flops=2 * n * f.top * W * 2 * f.ff, like="gemm routed gate|up")
+        rf = ret.mlp
+        _, rgo, rpt, _, _ = Q.moe_route(h, rw["router"], rf.top)
+        ms = timer(lambda: Q.gemm(h, rw["gu"], groups=rf.experts, n=rf.ff, dual=True, limit=rf.limit, grp_off=rgo, row_src=rpt,
+                                  rows=n * rf.top, max_rows=n))
+        add(f"radanex gemm routed gate|up + clamped glu, {rf.experts} experts top {rf.top} ({tag})", ms,
+            nbytes=min(rf.experts, n * rf.top) * 2 * rf.ff * W * 2 + n * W * 2 + n * rf.top * rf.ff * 2, flops=2 * n * rf.top * W * 2 * rf.ff)
+        # routers
+        ms = timer(lambda: Q.moe_route_ex(h, mw["router"], f.top, S.UMBS_ROUTE_SIGMOID_GROUPS, f.groups, f.keep))
+        add(f"router (sigmoid, {f.groups} groups keep {f.keep}) + expert sort ({tag})", ms, nbytes=n * W * 2, like="router + expert sort")
+        ms = timer(lambda: Q.moe_route(h, rw["router"], rf.top))
+        add(f"radanex router (softmax over the top) + expert sort ({tag})", ms, nbytes=n * W * 2)
+        ms = timer(lambda: Q.token_gate(h, mw["s_gate"]))
+        add(f"shared expert's gate per token ({tag})", ms, nbytes=n * W * 2)
+        # between in-projection and attention
+        cols = H * (D + Rt) + KD + H * V
+        proj = torch.randn(n, cols, device=device)
+        ms = timer(lambda: Q.latent_prep(proj, batch, H, D, Rt, R, mw["kv_norm"], sp.norm_eps, l.rot_dims, mw["inv_freq"], l.rot_mag,
+                                         torch.bfloat16))
+        add(f"latent norm + rotary of the shared key part and of every head's query ({tag})", ms,
+            nbytes=n * (H * (D + Rt) + KD) * (4 + 2) + n * H * Rt * 4, like="latent norm")
+        rproj = torch.randn(n, lat.q_rank + lat.kv_rank, device=device)
+        ms = timer(lambda: Q.latent_norm(rproj, lat.q_rank, lat.kv_rank, lw["q_norm"], lw["kv_norm"], rsp.norm_eps, torch.bfloat16))
+        add(f"radanex latent norm of the query and key latents ({tag})", ms, nbytes=n * (lat.q_rank + lat.kv_rank) * (4 + 2))
+        # attention
+        ring = km.cache.ring[1]
+        keys = sum(p + 1 for p in range(pos0, pos0 + per)) * nseq
+        gate = proj[:, H * (D + Rt) + KD:]
+        RR = lat.kv_rank
+        lring = rm.cache.ring[rsp.layers.index(lat)]
+        rkeys = sum(min(p + 1, lat.window) for p in range(pos0, pos0 + per)) * nseq
+        if n == T:
+            q, kvh, ks = torch.randn(n, H * (D + Rt), **bf), torch.randn(n, H * (D + V), **bf), torch.randn(n, KD, **bf)
+            ms = timer(lambda: Q.window_attention_shared(q, kvh[:, :H * D], ks[:, R:], kvh[:, H * D:], batch, H, l.scale, sink=mw["sink"],
+                                                         gate=gate))
+            add(f"attention over per-head keys + shared rotated part, causal, sink, gate, fp32 scores ({tag})", ms,
+                nbytes=n * (H * (D + Rt) + H * (D + V) + Rt + H * V) * 2 + n * H * V * 4, flops32=2 * keys * H * (D + Rt + V),
+                like="window attention over per-head keys")
+            hd, hvv = lat.heads * lat.dim, lat.heads * lat.vdim
+            qh, kv2 = torch.randn(n, hd, **bf), torch.randn(n, hd + hvv, **bf)
+            ms = timer(lambda: Q.window_attention(qh, kv2[:, :hd], kv2[:, hd:], batch, lat.heads, lat.window, lat.scale))
+            add(f"radanex window attention over per-head keys, window {lat.window}, fp32 scores ({tag})", ms,
+                nbytes=n * (2 * hd + 2 * hvv) * 2, flops32=2 * rkeys * lat.heads * (lat.dim + lat.vdim))
+        qa, c = torch.randn(n, H, KD, device=device), torch.randn(n, KD, **bf)
+        ms = timer(lambda: Q.latent_attention_shared(qa, c, ring, batch, H, R, Rt, l.scale, sink=mw["sink"], append=False))
+        add(f"latent attention over [latent | shared part] keys, causal, sink, fp32 scores ({tag})", ms,
+            nbytes=n * H * (KD * 4 + R * 2) + (n * KD * 2 if n == T else keys * KD * 2), flops32=2 * keys * H * (KD + R),
+            like="latent attention")
+        qr, cr = torch.randn(n, lat.heads * RR, device=device), torch.randn(n, RR, **bf)
+        ms = timer(lambda: Q.latent_attention(qr, cr, lring, batch, lat.heads, lat.window, lat.scale, append=False))
+        add(f"radanex latent attention, window {lat.window}, fp32 scores ({tag})", ms,
+            nbytes=n * lat.heads * RR * 6 + (n * RR * 2 if n == T else rkeys * RR * 2), flops32=4 * rkeys * lat.heads * RR)
+        # value up-projection per head with the output gate in the epilogue
+        o_lat = torch.randn(n, H * R, **bf)
+        uv = mw["uv"].view(H, V, R)
+        ms = timer(lambda: Q.gemm_ex(o_lat, uv, groups=H, a_goff=R, c_goff=V, n=V, k=R, out_gate=gate, gate_goff=V))
+        add(f"gemm value up-projection per head + sigmoid output gate ({tag})", ms,
+            nbytes=n * H * R * 2 + H * V * R * 2 + n * H * V * (2 + 4), flops=2 * n * H * V * R, like="gemm per head")
+        ro = torch.randn(n, lat.heads * RR, **bf)
+        ruv = lw["uv"].view(lat.heads, lat.vdim, RR)
+        ms = timer(lambda: Q.gemm(ro, ruv, groups=lat.heads, a_goff=RR, c_goff=lat.vdim, n=lat.vdim, k=RR))
+        add(f"radanex gemm value up-projection per head ({tag})", ms,
+            nbytes=n * lat.heads * RR * 2 + lat.heads * lat.vdim * RR * 2 + n * lat.heads * lat.vdim * 2, flops=2 * n * lat.heads * lat.vdim * RR)
+    return rows, how
+
+
+def run_kulisun(args):
+    from . import _lib_seq
+    device = "cuda:0"
+    timer = Timer(device)
+    hbm, tflops, how = _peaks()
+    sizes, table = [], None
+    launches0 = _lib_seq.load().umbs_launch_count()
+    for width in (1024, 2048):
+        layers, prompt, ctx = 8, 2048, 512
+        km, k = bench_kulisun(width, layers, device, prompt, ctx, (1, 8, 64), timer)
+        rm, r = bench_radanex(width, layers, device, prompt, ctx, (1, 8, 64), timer)
+        sizes.append({"width": width, "layers": layers, "kulisun_bf16": {a: round(v, 3) for a, v in k.items()},
+                      "radanex_bf16": {a: round(v, 3) for a, v in r.items()}})
+        if width == 2048:
+            table, _ = kernel_table_kulisun(km, rm, device, timer)
+        del km, rm
+        torch.cuda.empty_cache()
+    launches = _lib_seq.load().umbs_launch_count() - launches0
+    head = sizes[-1]["kulisun_bf16"]
+    line = {"metric": "decode tokens/sec at batch 64 (Kulisun bf16, width 2048, 8 layers, synthetic weights)",
+            "value": head["decode_b64_tok_s"], "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic", "vs_baseline": None, "gpu_launches": int(launches),
+            "config": {"name": "kulisun", "workload": "prefill 1 x 2048 and 4 x 2048 tokens; decode at batch 1 / 8 / 64 behind a "
+                       "512-token context; Radanex bf16 of the same width, depth and active feed-forward size beside it",
+                       "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": how},
+                       "l2": "whole-model runs stream more than L2 per step; kernel table flushes L2 between runs"},
+            "sizes": sizes, "kernels": table}
+    print(json.dumps(line))
