@@ -1,7 +1,7 @@
-"""One prefill step and a few eager decode steps of a synthetic Radanex (or Zedotar) model: the program to put under
+"""One prefill step and a few eager decode steps of a synthetic Radanex (or Zedotar, or Kulisun) model: the program to put under
 `ncu --metrics gpu__time_duration.sum` for a launch list of the sequence-state step (small: < 1 GB on the device).
 
-    python scripts/seq_step_once.py [width] [batch] [context] [decode steps] [radanex|zedotar]
+    python scripts/seq_step_once.py [width] [batch] [context] [decode steps] [radanex|zedotar|kulisun]
 """
 import os
 import sys
@@ -15,6 +15,9 @@ width, batch, ctx, steps = (int(x) for x in (sys.argv[1:5] + ["1024", "1", "512"
 if len(sys.argv) > 5 and sys.argv[5] == "zedotar":
     from umbrella_b200.models.zedotar import Zedotar as Family, spec_from_config  # noqa: E402
     spec = spec_from_config(seq_bench.zedotar_config(width, 8))
+elif len(sys.argv) > 5 and sys.argv[5] == "kulisun":
+    from umbrella_b200.models.kulisun import Kulisun as Family, spec_from_config  # noqa: E402
+    spec = spec_from_config(seq_bench.kulisun_config(width, 8))
 else:
     from umbrella_b200.models.radanex import Radanex as Family, spec_from_config  # noqa: E402
     spec = spec_from_config(seq_bench.radanex_config(width, 8))

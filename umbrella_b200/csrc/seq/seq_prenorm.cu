@@ -99,12 +99,21 @@ __global__ void add_norm_kernel(float* __restrict__ x, umbs_delta_t d, int has_d
                                 const float* __restrict__ w, const float* __restrict__ bias, float w_offset, int width, float eps,
                                 T* __restrict__ y, float* __restrict__ copy) {
     __shared__ float red[33];
+    constexpr int KEEP = 8, TOPS = 16;              // up to TOPS routed pairs per token are held in shared memory
+    __shared__ float s_w[TOPS];
+    __shared__ const float* s_p[TOPS];
     const int r = blockIdx.x;
     const int64_t src = rows ? rows[r] : r;
     float* xr = x + src * width;
-    constexpr int KEEP = 8;
     float v[KEEP];
     const float sg = (has_d && d.shared != nullptr && d.shared_gate != nullptr) ? d.shared_gate[src] : 1.f;
+    const bool routed = has_d && d.pair_out != nullptr;
+    const int top_s = routed ? min(d.top, TOPS) : 0;
+    if (threadIdx.x < top_s) {                      // the token's weights and the rows of its experts' outputs, read once
+        s_w[threadIdx.x] = d.sel_w[src * d.top + threadIdx.x];
+        s_p[threadIdx.x] = d.pair_out + (int64_t)d.pair_pos[src * d.top + threadIdx.x] * width;
+    }
+    if (routed) __syncthreads();
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < KEEP; ++i) {
@@ -114,9 +123,10 @@ __global__ void add_norm_kernel(float* __restrict__ x, umbs_delta_t d, int has_d
             float dl = 0.f;
             if (has_d) {
                 if (d.delta != nullptr) dl = d.delta[src * width + e];
-                if (d.pair_out != nullptr) {
+                if (routed) {
                     float ff = 0.f;
-                    for (int k = 0; k < d.top; ++k)
+                    for (int k = 0; k < top_s; ++k) ff = fmaf(s_w[k], s_p[k][e], ff);
+                    for (int k = top_s; k < d.top; ++k)
                         ff = fmaf(d.sel_w[src * d.top + k], d.pair_out[(int64_t)d.pair_pos[src * d.top + k] * width + e], ff);
                     dl += ff;
                 }

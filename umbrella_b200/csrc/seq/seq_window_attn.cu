@@ -34,15 +34,18 @@ template <typename T, int VC>
 __global__ void __launch_bounds__(256) window_attention_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k,
                                                                int64_t ldk, const T* __restrict__ v, int64_t ldv, Batch b,
                                                                int dim, int vdim, int window, float scale,
-                                                               T* __restrict__ out, int64_t ldo, WindowExtra x) {
+                                                               T* __restrict__ out, int64_t ldo, WindowExtra x, int kc) {
+    // kc: dimensions of a key tile held at a time (all of them up to 64; larger heads add their scores up over several
+    // passes and keep the weights where the key tile was, which leaves room for two blocks on an SM)
     extern __shared__ __align__(16) float sm[];
     const T* ks = (const T*)x.ks;
     const int kdim = x.kdim;
+    const bool alias_p = kc < dim;
     constexpr int VW = 16 * VC, VP = VW + 4;          // value columns a block covers; row stride of the value tile
     float* Qs = sm;                                   // [dim][kWaS]  Qs[d][row]
-    float* Ks = Qs + (size_t)dim * kWaS;              // [dim][kWaS]  Ks[d][key]
-    float* Vs = Ks + (size_t)dim * kWaS;              // [kWaK][VP]
-    float* Ps = Vs + (size_t)kWaK * VP;               // [kWaK][kWaS] Ps[key][row]
+    float* Ks = Qs + (size_t)dim * kWaS;              // [kc][kWaS]   Ks[d][key]
+    float* Vs = Ks + (size_t)kc * kWaS;               // [kWaK][VP]
+    float* Ps = alias_p ? Ks : Vs + (size_t)kWaK * VP;   // [kWaK][kWaS] Ps[key][row]
     const int s = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * kWaQ;
     const int len = b.seq_len[s], start = b.seq_start[s];
     if (q0 >= len) return;
@@ -61,34 +64,38 @@ __global__ void __launch_bounds__(256) window_attention_kernel(const T* __restri
     }
     const int row_hi = min(len, q0 + kWaQ) - 1;       // last row of the block = last key any of its rows sees
     for (int j0 = max(0, q0 - window + 1); j0 <= row_hi; j0 += kWaK) {
-        __syncthreads();                              // the previous tile is consumed (first time round: Qs is written)
-        for (int i = tid; i < kWaK * dim; i += 256) {
-            const int kk = i / dim, d = i - kk * dim, j = j0 + kk;
-            float kvl = 0.f;
-            if (j <= row_hi)
-                kvl = d < kdim ? to_f32(k[(int64_t)(start + j) * ldk + (int64_t)h * kdim + d])
-                               : to_f32(ks[(int64_t)(start + j) * x.ldks + (d - kdim)]);
-            Ks[d * kWaS + kk] = kvl;
-        }
-        for (int i = tid; i < kWaK * VW; i += 256) {
-            const int kk = i / VW, c = i - kk * VW, j = j0 + kk;
-            Vs[kk * VP + c] = (j <= row_hi && c < vdim) ? to_f32(v[(int64_t)(start + j) * ldv + (int64_t)h * vdim + c]) : 0.f;
-        }
-        __syncthreads();
         float sc[4][4];
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) sc[i][jj] = 0.f;
-        for (int d = 0; d < dim; ++d) {
-            const float4 qv = *reinterpret_cast<const float4*>(Qs + d * kWaS + ty * 4);
-            const float4 kv = *reinterpret_cast<const float4*>(Ks + d * kWaS + tx * 4);
-            const float qa[4] = {qv.x, qv.y, qv.z, qv.w}, ka[4] = {kv.x, kv.y, kv.z, kv.w};
+        for (int d0 = 0; d0 < dim; d0 += kc) {
+            const int dc = min(kc, dim - d0);
+            __syncthreads();                          // the previous pass or tile is consumed (first time round: Qs is written)
+            for (int i = tid; i < kWaK * dc; i += 256) {
+                const int kk = i / dc, d = d0 + i - kk * dc, j = j0 + kk;
+                float kvl = 0.f;
+                if (j <= row_hi)
+                    kvl = d < kdim ? to_f32(k[(int64_t)(start + j) * ldk + (int64_t)h * kdim + d])
+                                   : to_f32(ks[(int64_t)(start + j) * x.ldks + (d - kdim)]);
+                Ks[(d - d0) * kWaS + kk] = kvl;
+            }
+            for (int i = tid; d0 == 0 && i < kWaK * VW; i += 256) {
+                const int kk = i / VW, c = i - kk * VW, j = j0 + kk;
+                Vs[kk * VP + c] = (j <= row_hi && c < vdim) ? to_f32(v[(int64_t)(start + j) * ldv + (int64_t)h * vdim + c]) : 0.f;
+            }
+            __syncthreads();
+            for (int d = 0; d < dc; ++d) {
+                const float4 qv = *reinterpret_cast<const float4*>(Qs + (d0 + d) * kWaS + ty * 4);
+                const float4 kv = *reinterpret_cast<const float4*>(Ks + d * kWaS + tx * 4);
+                const float qa[4] = {qv.x, qv.y, qv.z, qv.w}, ka[4] = {kv.x, kv.y, kv.z, kv.w};
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+                for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int jj = 0; jj < 4; ++jj) sc[i][jj] = fmaf(qa[i], ka[jj], sc[i][jj]);
+                    for (int jj = 0; jj < 4; ++jj) sc[i][jj] = fmaf(qa[i], ka[jj], sc[i][jj]);
+            }
         }
+        if (alias_p) __syncthreads();                 // the weights go where the last key pass sits
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int rp = q0 + ty * 4 + i;           // the row's index in its sequence; only differences to keys matter
@@ -161,7 +168,8 @@ template <typename T, int VC>
 static int launch_window_attention(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
                                    const Batch& b, int heads, int dim, int vdim, int window, float scale, void* out,
                                    int64_t ldo, const WindowExtra& x, cudaStream_t st) {
-    const size_t smem = ((size_t)2 * dim * kWaS + (size_t)kWaK * (16 * VC + 4) + (size_t)kWaK * kWaS) * sizeof(float);
+    const int kc = dim <= 64 ? dim : 64;
+    const size_t smem = ((size_t)(dim + kc) * kWaS + (size_t)kWaK * (16 * VC + 4) + (kc < dim ? 0 : (size_t)kWaK * kWaS)) * sizeof(float);
     static size_t set = 0;
     if (smem > 48 * 1024 && smem > set) {
         cudaError_t e = cudaFuncSetAttribute(window_attention_kernel<T, VC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -171,7 +179,7 @@ static int launch_window_attention(const void* q, int64_t ldq, const void* k, in
     }
     const dim3 grid((b.max_seq_len + kWaQ - 1) / kWaQ, heads, b.n_seqs);
     window_attention_kernel<T, VC><<<grid, 256, smem, st>>>((const T*)q, ldq, (const T*)k, ldk, (const T*)v, ldv, b, dim, vdim,
-                                                            window, scale, (T*)out, ldo, x);
+                                                            window, scale, (T*)out, ldo, x, kc);
     return 0;
 }
 

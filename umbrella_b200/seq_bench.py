@@ -23,17 +23,18 @@ def _peaks():
         return 6650.0, 1590.0, "fallback"
 
 
-def radanex_config(width: int, layers: int = 8) -> dict:
-    """A Radanex config with the layer sizes of a model of this width: every fourth layer latent attention."""
+def radanex_config(width: int, layers: int = 8, latent_every: int = 4, window: int = 1024) -> dict:
+    """A Radanex config with the layer sizes of a model of this width: every fourth layer latent attention (or every
+    ``latent_every``-th, over the last ``window`` tokens)."""
     heads = width // 128
     ret = dict(type="retention", mixer=dict(heads=heads, dim=64, vdim=128, rot=dict(dims=64, base=1e6),
                                            decay=[1 - 2.0 ** (-5 - (3 * h) // heads) for h in range(heads)]))
     lat = dict(type="latent_attention", mixer=dict(heads=heads, dim=64, vdim=128, q_rank=3 * width // 8, kv_rank=width // 4,
-                                                   scale=0.125, mask=dict(size=1024)))
+                                                   scale=0.125, mask=dict(size=window)))
     mlp = dict(kind="moe", router=dict(experts=16, top=2), expert=dict(ff=width // 2, limit=7.0),
                shared=dict(ff=width, limit=7.0))
     return dict(architecture="Radanex", width=width, vocab=32768, norm=dict(eps=1e-6, groups=4),
-                layers=[dict(lat if i % 4 == 3 else ret, mlp=mlp) for i in range(layers)])
+                layers=[dict(lat if i % latent_every == latent_every - 1 else ret, mlp=mlp) for i in range(layers)])
 
 
 class Timer:
@@ -74,9 +75,9 @@ def zedotar_config(width: int, layers: int = 8) -> dict:
                 layers=[dict(k, mlp=mlp) for k in kinds])
 
 
-def bench_radanex(width, layers, device, prompt, ctx, batches, timer):
+def bench_radanex(width, layers, device, prompt, ctx, batches, timer, **config):
     from .models.radanex import Radanex, spec_from_config
-    spec = spec_from_config(radanex_config(width, layers))
+    spec = spec_from_config(radanex_config(width, layers, **config))
     m = Radanex(spec, device=device, dtype=torch.bfloat16, slots=max(batches))
     return bench_seq_model(m, spec, prompt, ctx, batches, timer)
 
@@ -610,8 +611,12 @@ def run_kulisun(args):
         layers, prompt, ctx = 8, 2048, 512
         km, k = bench_kulisun(width, layers, device, prompt, ctx, (1, 8, 64), timer)
         rm, r = bench_radanex(width, layers, device, prompt, ctx, (1, 8, 64), timer)
-        sizes.append({"width": width, "layers": layers, "kulisun_bf16": {a: round(v, 3) for a, v in k.items()},
-                      "radanex_bf16": {a: round(v, 3) for a, v in r.items()}})
+        # the closest shape the existing family takes: latent attention in every layer, over the whole context
+        ra, a = bench_radanex(width, layers, device, prompt, ctx, (1, 8, 64), timer, latent_every=1, window=4096)
+        del ra
+        sizes.append({"width": width, "layers": layers, "kulisun_bf16": {a_: round(v, 3) for a_, v in k.items()},
+                      "radanex_bf16": {a_: round(v, 3) for a_, v in r.items()},
+                      "radanex_all_latent_bf16": {a_: round(v, 3) for a_, v in a.items()}})
         if width == 2048:
             table, _ = kernel_table_kulisun(km, rm, device, timer)
         del km, rm
@@ -622,7 +627,9 @@ def run_kulisun(args):
             "value": head["decode_b64_tok_s"], "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
             "data": "synthetic", "vs_baseline": None, "gpu_launches": int(launches),
             "config": {"name": "kulisun", "workload": "prefill 1 x 2048 and 4 x 2048 tokens; decode at batch 1 / 8 / 64 behind a "
-                       "512-token context; Radanex bf16 of the same width, depth and active feed-forward size beside it",
+                       "512-token context; Radanex bf16 of the same width, depth and active feed-forward size beside it, as "
+                       "packaged (latent attention in every fourth layer, window 1024) and with latent attention in every layer "
+                       "over the whole context",
                        "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": how},
                        "l2": "whole-model runs stream more than L2 per step; kernel table flushes L2 between runs"},
             "sizes": sizes, "kernels": table}
