@@ -46,7 +46,8 @@ __global__ void __launch_bounds__(256) window_attention_kernel(const T* __restri
     float* Ks = Qs + (size_t)dim * kWaS;              // [kc][kWaS]   Ks[d][key]
     float* Vs = Ks + (size_t)kc * kWaS;               // [kWaK][VP]
     float* Ps = alias_p ? Ks : Vs + (size_t)kWaK * VP;   // [kWaK][kWaS] Ps[key][row]
-    const int s = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * kWaQ;
+    // the last row tiles see the most keys: they are handed out first, so that the short ones fill the tail of the grid
+    const int s = blockIdx.z, h = blockIdx.y, q0 = (int)(gridDim.x - 1 - blockIdx.x) * kWaQ;
     const int len = b.seq_len[s], start = b.seq_start[s];
     if (q0 >= len) return;
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
