@@ -309,10 +309,11 @@ int umbs_moe_route(int dtype, const void* h, int n, int width, const float* w_ro
                    umbs_stream_t stream);
 
 /* umbs_moe_route with the rule as an argument (mode: UMBS_ROUTE_*; groups, keep: see UMBS_ROUTE_SIGMOID_GROUPS; at most 64
- * groups).  Ties go to the lower index. */
+ * groups).  Ties go to the lower index.  gate_w (fp32 [width], or NULL): one more row beside the router's, whose sigmoid
+ * goes to gate_out[t] (fp32 [n]) -- what umbs_token_gate computes, in the same pass over h. */
 int umbs_moe_route_ex(int dtype, const void* h, int n, int width, const float* w_router, int experts, int top, int mode,
                       int groups, int keep, float* sel_w, int32_t* grp_off, int32_t* pair_tok, int32_t* pair_pos,
-                      int32_t* scratch, umbs_stream_t stream);
+                      int32_t* scratch, const float* gate_w, float* gate_out, umbs_stream_t stream);
 
 /* g[t] = sigmoid(w . h[t]) in fp32; h: `dtype` [n, width], w: fp32 [width]. */
 int umbs_token_gate(int dtype, const void* h, int n, int width, const float* w, float* g, umbs_stream_t stream);

@@ -117,7 +117,11 @@ def test_group_limited_sigmoid_router(n):
     for E, G, keep, top in ((12, 3, 2, 4), (8, 8, 3, 2), (6, 1, 1, 6), (10, 5, 5, 1), (16, 4, 1, 4)):
         h, wr = rnd(n, 48, seed=E), rnd(E, 48, seed=E + 1, scale=0.4)
         chosen, weights = O.route(h, dict(router=wr, groups=G, keep=keep, top=top))
-        sel_w, grp_off, pair_tok, pair_pos, sel_e = K.moe_route_ex(f32(h), f32(wr), top, S.UMBS_ROUTE_SIGMOID_GROUPS, G, keep)
+        gw = rnd(48, seed=E + 2, scale=0.4)          # the per-token gate rides along in the same pass
+        sel_w, grp_off, pair_tok, pair_pos, sel_e, gate = K.moe_route_ex(f32(h), f32(wr), top, S.UMBS_ROUTE_SIGMOID_GROUPS, G, keep,
+                                                                         gate_w=f32(gw))
+        assert err(gate, torch.sigmoid(h @ gw)) < 2e-6
+        assert torch.equal(gate, K.token_gate(f32(h), f32(gw)))
         sel_e, sel_w = sel_e.cpu(), sel_w.cpu()
         for t in range(n):
             assert sel_e[t].tolist() == chosen[t], (E, G, keep, top, t)
@@ -190,7 +194,7 @@ def run_latent(q_abs, c, R, Rt, scale, sink, pieces, slot=0, ring=None, cap=None
     return torch.cat(out).view(n, H, R), ring
 
 
-@pytest.mark.parametrize("H,R,Rt", [(4, 40, 8), (1, 33, 0), (8, 128, 16), (3, 20, 12)])
+@pytest.mark.parametrize("H,R,Rt", [(4, 40, 8), (1, 33, 0), (6, 120, 24), (3, 20, 12)])
 def test_latent_attention_whole_portions_and_decode(H, R, Rt):
     n, scale = 150, 0.2
     q_abs, c, sink = rnd(n, H, R + Rt, seed=1), rnd(n, R + Rt, seed=2), rnd(H, seed=3, scale=1.5)

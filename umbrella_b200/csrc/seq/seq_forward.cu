@@ -249,8 +249,10 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
             pend = umbs_delta_t{};
             pend.scale = l.out_scale2; pend.mult = mult;
             if (f.experts > 0) {
+                // (the shared expert's per-token gate rides along as one more row of the router)
                 UMBS_TRY(umbs_moe_route_ex(dt, s.h, T, W, f.w_router, f.experts, f.top, f.route_mode, f.groups, f.keep, s.sel_w,
-                                           s.grp_off, s.pair_tok, s.pair_pos, s.route_scratch, stream));
+                                           s.grp_off, s.pair_tok, s.pair_pos, s.route_scratch,
+                                           f.shared_ff > 0 ? f.w_shared_gate : nullptr, s.sgate, stream));
                 UMBS_TRY(umbs_gemm(dt, s.h, W, 0, f.w_gu, W, (int64_t)2 * f.ff * W, s.y, f.ff, 0, 0, T, f.ff, W, f.experts,
                                    s.grp_off, s.pair_tok, act, f.limit, stream));
                 UMBS_TRY(umbs_gemm(dt, s.y, f.ff, 0, f.w_down, f.ff, (int64_t)W * f.ff, s.pair_out, W, 0, 1, T, W, f.ff, f.experts,
@@ -262,7 +264,7 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
                                       act, f.shared_limit, f.bias_gu, nullptr, 0, 0, stream));
                 UMBS_TRY(umbs_gemm_ex(dt, s.ys, f.shared_ff, 0, f.ws_down, f.shared_ff, 0, s.shared_out, W, 0, 1, T, W, f.shared_ff, 1,
                                       nullptr, nullptr, 0, 0.f, f.bias_down, nullptr, 0, 0, stream));
-                if (f.w_shared_gate != nullptr) UMBS_TRY(umbs_token_gate(dt, s.h, T, W, f.w_shared_gate, s.sgate, stream));
+                if (f.w_shared_gate != nullptr && f.experts <= 0) UMBS_TRY(umbs_token_gate(dt, s.h, T, W, f.w_shared_gate, s.sgate, stream));
                 if (f.experts > 0 || f.w_shared_gate != nullptr) {
                     pend.shared = s.shared_out;
                     pend.shared_gate = f.w_shared_gate != nullptr ? s.sgate : nullptr;

@@ -632,14 +632,19 @@ template <typename T>
 __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ h, int n, int width, const float* __restrict__ wr,
                                                          int experts, int top, int mode, int groups, int keep,
                                                          float* __restrict__ sel_w, int32_t* __restrict__ sel_e,
-                                                         int32_t* __restrict__ counts) {
+                                                         int32_t* __restrict__ counts, const float* __restrict__ gate_w,
+                                                         float* __restrict__ gate_out) {
     extern __shared__ float z[];           // [experts]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int t = blockIdx.x;
     const T* hr = h + (int64_t)t * width;
-    for (int e = warp; e < experts; e += nw) {
-        const float s = router_logit(hr, wr + (int64_t)e * width, width, lane);
-        if (lane == 0) z[e] = s;
+    for (int e = warp; e < experts + (gate_w != nullptr ? 1 : 0); e += nw) {
+        // one more row for the token's gate (the shared expert's factor): sigmoid of its logit
+        const float s = router_logit(hr, e < experts ? wr + (int64_t)e * width : gate_w, width, lane);
+        if (lane == 0) {
+            if (e < experts) z[e] = s;
+            else gate_out[t] = 1.f / (1.f + expf(-s));
+        }
     }
     __syncthreads();
     if (threadIdx.x == 0)
@@ -655,7 +660,8 @@ __global__ void __launch_bounds__(1024) moe_route_small_kernel(const T* __restri
                                                               int mode, int groups, int keep,
                                                               float* __restrict__ sel_w, int32_t* __restrict__ sel_e,
                                                               int32_t* __restrict__ grp_off, int32_t* __restrict__ pair_tok,
-                                                              int32_t* __restrict__ pair_pos) {
+                                                              int32_t* __restrict__ pair_pos, const float* __restrict__ gate_w,
+                                                              float* __restrict__ gate_out) {
     extern __shared__ float zs[];                    // [n][experts] logits, then [experts] counts, [n top] chosen experts
     int32_t* counts = reinterpret_cast<int32_t*>(zs + n * experts);
     int32_t* offs = counts + experts;                // [experts + 1]
@@ -666,6 +672,10 @@ __global__ void __launch_bounds__(1024) moe_route_small_kernel(const T* __restri
         const int t = i / experts, e = i - t * experts;
         const float s = router_logit(h + (int64_t)t * width, wr + (int64_t)e * width, width, lane);
         if (lane == 0) zs[i] = s;
+    }
+    for (int t = warp; gate_w != nullptr && t < n; t += nw) {
+        const float s = router_logit(h + (int64_t)t * width, gate_w, width, lane);
+        if (lane == 0) gate_out[t] = 1.f / (1.f + expf(-s));
     }
     __syncthreads();
     for (int t = threadIdx.x; t < n; t += blockDim.x)
@@ -982,14 +992,15 @@ extern "C" int umbs_moe_route(int dtype, const void* h, int n, int width, const 
                               float* sel_w, int32_t* grp_off, int32_t* pair_tok, int32_t* pair_pos, int32_t* scratch,
                               umbs_stream_t stream) {
     return umbs_moe_route_ex(dtype, h, n, width, w_router, experts, top, UMBS_ROUTE_SOFTMAX_TOP, 1, 1, sel_w, grp_off, pair_tok,
-                             pair_pos, scratch, stream);
+                             pair_pos, scratch, nullptr, nullptr, stream);
 }
 
 extern "C" int umbs_moe_route_ex(int dtype, const void* h, int n, int width, const float* w_router, int experts, int top,
                                  int mode, int groups, int keep, float* sel_w, int32_t* grp_off, int32_t* pair_tok,
-                                 int32_t* pair_pos, int32_t* scratch, umbs_stream_t stream) {
+                                 int32_t* pair_pos, int32_t* scratch, const float* gate_w, float* gate_out,
+                                 umbs_stream_t stream) {
     if (n <= 0) return 0;
-    if (top < 1 || top > experts) return UMB_ERR_ARG;
+    if (top < 1 || top > experts || (gate_w != nullptr && gate_out == nullptr)) return UMB_ERR_ARG;
     if (mode == UMBS_ROUTE_SIGMOID_GROUPS) {
         if (groups < 1 || experts % groups != 0 || keep < 1 || keep > groups || top > keep * (experts / groups)) return UMB_ERR_ARG;
         if (groups > 64) return UMB_ERR_UNSUPPORTED;
@@ -1002,7 +1013,7 @@ extern "C" int umbs_moe_route_ex(int dtype, const void* h, int n, int width, con
         const size_t smem = ((size_t)n * experts + 2 * (size_t)experts + 1 + (size_t)n * top) * sizeof(float);
         UMBS_DISPATCH_T(dtype, moe_route_small_kernel<T><<<1, 1024, smem, st>>>((const T*)h, n, width, w_router, experts, top,
                                                                               mode, groups, keep, sel_w, scratch + 2 * experts,
-                                                                              grp_off, pair_tok, pair_pos));
+                                                                              grp_off, pair_tok, pair_pos, gate_w, gate_out));
         count_launches(1);
         return (int)cudaGetLastError();
     }
@@ -1013,7 +1024,8 @@ extern "C" int umbs_moe_route_ex(int dtype, const void* h, int n, int width, con
     if (e != cudaSuccess) return (int)e;
     const int rthreads = experts >= 8 ? 256 : 32 * experts;
     UMBS_DISPATCH_T(dtype, moe_router_kernel<T><<<n, rthreads, (size_t)experts * sizeof(float), st>>>(
-                               (const T*)h, n, width, w_router, experts, top, mode, groups, keep, sel_w, sel_e, counts));
+                               (const T*)h, n, width, w_router, experts, top, mode, groups, keep, sel_w, sel_e, counts, gate_w,
+                               gate_out));
     moe_offsets_kernel<<<1, 32, 0, st>>>(counts, experts, grp_off, cursor);
     const int pairs = n * top;
     moe_scatter_kernel<<<(pairs + 255) / 256, 256, 0, st>>>(sel_e, pairs, top, grp_off, cursor, pair_tok, pair_pos);

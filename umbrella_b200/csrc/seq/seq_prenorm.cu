@@ -114,6 +114,19 @@ __global__ void add_norm_kernel(float* __restrict__ x, umbs_delta_t d, int has_d
         s_p[threadIdx.x] = d.pair_out + (int64_t)d.pair_pos[src * d.top + threadIdx.x] * width;
     }
     if (routed) __syncthreads();
+    // the routed experts' rows first, expert by expert: the thread's eight loads of a row are in flight together
+    float ff[KEEP];
+#pragma unroll
+    for (int i = 0; i < KEEP; ++i) ff[i] = 0.f;
+    for (int k = 0; routed && k < d.top; ++k) {
+        const float wk = k < top_s ? s_w[k] : d.sel_w[src * d.top + k];
+        const float* pk = k < top_s ? s_p[k] : d.pair_out + (int64_t)d.pair_pos[src * d.top + k] * width;
+#pragma unroll
+        for (int i = 0; i < KEEP; ++i) {
+            const int e = threadIdx.x + i * blockDim.x;
+            if (e < width) ff[i] = fmaf(wk, pk[e], ff[i]);
+        }
+    }
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < KEEP; ++i) {
@@ -123,13 +136,7 @@ __global__ void add_norm_kernel(float* __restrict__ x, umbs_delta_t d, int has_d
             float dl = 0.f;
             if (has_d) {
                 if (d.delta != nullptr) dl = d.delta[src * width + e];
-                if (routed) {
-                    float ff = 0.f;
-                    for (int k = 0; k < top_s; ++k) ff = fmaf(s_w[k], s_p[k][e], ff);
-                    for (int k = top_s; k < d.top; ++k)
-                        ff = fmaf(d.sel_w[src * d.top + k], d.pair_out[(int64_t)d.pair_pos[src * d.top + k] * width + e], ff);
-                    dl += ff;
-                }
+                dl += ff[i];
                 if (d.shared != nullptr) dl = fmaf(d.shared[src * width + e], sg, dl);
                 if (d.scale != nullptr) dl *= d.scale[e];
                 dl *= d.mult;

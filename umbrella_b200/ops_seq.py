@@ -319,8 +319,9 @@ def window_attention_shared(q, k, k_shared, v, batch: RaggedBatch, heads: int, s
     return out
 
 
-def moe_route_ex(h, w_router, top: int, mode: int, groups: int = 1, keep: int = 1):
-    """``moe_route`` with the rule as an argument (UMBS_ROUTE_*)."""
+def moe_route_ex(h, w_router, top: int, mode: int, groups: int = 1, keep: int = 1, gate_w=None):
+    """``moe_route`` with the rule as an argument (UMBS_ROUTE_*).  With ``gate_w`` the per-token gate sigmoid(gate_w . h) is
+    worked out in the same pass and returned as a sixth value."""
     n, width = h.shape
     E = w_router.shape[0]
     dev = h.device
@@ -329,9 +330,12 @@ def moe_route_ex(h, w_router, top: int, mode: int, groups: int = 1, keep: int = 
     pair_tok = torch.empty(n * top, dtype=torch.int32, device=dev)
     pair_pos = torch.empty(n * top, dtype=torch.int32, device=dev)
     scratch = torch.empty(2 * E + n * top, dtype=torch.int32, device=dev)
+    gate = torch.empty(n, dtype=torch.float32, device=dev) if gate_w is not None else None
     S.check(S.load().umbs_moe_route_ex(_mode(h), _p(h), n, width, _p(w_router), E, top, mode, groups, keep, _p(sel_w),
-                                       _p(grp_off), _p(pair_tok), _p(pair_pos), _p(scratch), _stream()), "moe_route_ex")
-    return sel_w, grp_off, pair_tok, pair_pos, scratch[2 * E:].view(n, top)
+                                       _p(grp_off), _p(pair_tok), _p(pair_pos), _p(scratch), _p(gate_w), _p(gate), _stream()),
+            "moe_route_ex")
+    out = (sel_w, grp_off, pair_tok, pair_pos, scratch[2 * E:].view(n, top))
+    return out + (gate,) if gate_w is not None else out
 
 
 def token_gate(h, w):
