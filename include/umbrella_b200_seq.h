@@ -12,7 +12,9 @@
  *
  * Models of the pre-norm form (UMBS_FORM_PRENORM) also keep what their mixers need in the slot: the key | value rows of
  * cached attention (a ring for a window, every token without one), one mean key | value row per block of older tokens,
- * the last projected rows in front of a short convolution, and the matrix memory of mLSTM layers.
+ * the last projected rows in front of a short convolution, and the matrix memory of mLSTM layers.  The latent-attention
+ * mixer also runs in this form, with direct queries, a rotated key part all heads share (kept behind the latent in the
+ * ring), a sink and an output gate; its ring holds the whole sequence when the layer has no window.
  *
  * The building blocks are exported on their own (umbs_group_norm_shift, umbs_retention, umbs_latent_attention,
  * umbs_moe_route, umbs_gemm, umbs_depth_mix ...), each with its constants as arguments, and umbs_forward chains

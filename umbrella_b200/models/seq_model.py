@@ -2,11 +2,12 @@
 
 A model is a ``SeqModelSpec``: width, vocabulary, the norm's constants and a list of ``SeqLayerSpec``s, each naming
 its form (``"parallel"``: one grouped norm feeds mixer and feed-forward side by side, with token shift and a depth
-average as options; ``"prenorm"``: x += mixer(norm1(x)), x += ff(norm2(x))), its mixer (``"retention"``,
-``"latent_attention"``, ``"cached_attention"`` or ``"mlstm"``) with that mixer's sizes and constants, and its
-feed-forward (routed experts and / or a shared expert -- a dense feed-forward is a shared expert alone -- or none).
-Model families (models/radanex.py, models/zedotar.py) translate their config.json into a spec and their tensors into
-the per-layer weight dicts ``load_layer`` takes; nothing below knows a family's names.
+average as options; ``"prenorm"``: x += mixer(norm1(x)), x += ff(norm2(x)), RMS or layer norms, optionally with a learned
+scale vector and a multiplier on every block's output), its mixer (``"retention"``, ``"latent_attention"``,
+``"cached_attention"`` or ``"mlstm"``) with that mixer's sizes and constants, and its feed-forward (routed experts and /
+or a shared expert -- a dense feed-forward is a shared expert alone -- or none).  Model families (models/radanex.py,
+models/zedotar.py, models/kulisun.py) translate their config.json into a spec and their tensors into the per-layer
+weight dicts ``load_layer`` takes; nothing below knows a family's names.
 
 One ``forward`` call runs a ragged batch: for every sequence its slot of the ``SequenceStateCache`` and its next
 tokens (any number: a whole prompt, a portion of one, one decoded token), and the places whose logits are wanted.
