@@ -43,6 +43,8 @@ typedef void* umbs_stream_t; /* cudaStream_t */
                                       * blocks of older keys, sink or sigmoid weights, short convolution on q and k,
                                       * values = unrotated keys, output gate per head or per element */
 #define UMBS_MIX_MLSTM 3             /* matrix memory with exponential gates and a running maximum */
+#define UMBS_MIX_TIME_MIX 4          /* matrix memory with a decay per key channel and token, computed from the token itself;
+                                      * five token-shifted mixes of the input feed its projections */
 
 /* How a layer is put together.  PARALLEL: one group norm feeds the mixer (token-shifted) and the feed-forward side by
  * side, the sum goes through the depth average.  PRENORM: x += mixer(norm1(x)), then x += ff(norm2(x)). */
@@ -54,15 +56,21 @@ typedef void* umbs_stream_t; /* cudaStream_t */
 #define UMBS_ACT_GELU_TANH 2         /* gelu_tanh(g) u */
 #define UMBS_ACT_SILU 3              /* g sigmoid(g) u */
 
+/* Activation of a plain product (the `unary` argument of umbs_gemm_unary; 0 = none). */
+#define UMBS_UNARY_TANH 1            /* tanh(z) */
+#define UMBS_UNARY_XIELU 2           /* z > 0: p0 z^2 + z / 2; z <= 0: p1 (exp(z) - 1 - z) + z / 2 */
+
 /* Norm of the pre-norm layer form. */
 #define UMBS_NORM_RMS 0              /* x / sqrt(mean(x^2) + eps) * (offset + w) */
 #define UMBS_NORM_LAYER 1            /* (x - mean) / sqrt(mean((x - mean)^2) + eps) * (offset + w) + b */
+#define UMBS_NORM_DYT 2              /* tanh(alpha x) * (offset + w) + b: no mean, no variance */
 
 /* How a router turns its logits into experts and weights. */
 #define UMBS_ROUTE_SOFTMAX_TOP 0     /* the `top` largest logits, softmax over them */
 #define UMBS_ROUTE_SIGMOID_GROUPS 1  /* scores sigmoid(z); the experts form `groups` equal groups of neighbours, a group
                                       * scores the sum of its two largest scores, only experts of the `keep` best groups are
                                       * eligible; the `top` largest eligible scores, divided by their sum (+ 1e-20) */
+#define UMBS_ROUTE_SOFTMAX_ALL 2     /* softmax over all experts; the `top` largest scores, as they are (not renormalised) */
 
 /* How attention turns scores into weights. */
 #define UMBS_ATTN_SOFTMAX 0          /* p = exp(s) / sum exp(s) */
@@ -105,9 +113,13 @@ typedef struct {
     const float* bias_gu;      /* fp32 [2 shared_ff] or NULL: biases of the shared (dense) gate rows, then of its up rows */
     const float* bias_down;    /* fp32 [width] or NULL: bias of the shared (dense) down projection */
     const float* w_shared_gate;/* fp32 [width] or NULL: the shared expert's output is multiplied by sigmoid(w . h), a number per token */
+    float route_scale;         /* factor on the chosen experts' weights (0 reads as 1) */
+    int plain;                 /* the shared (dense) part has no gate rows: W_down unary(W_up h), ws_gu = [shared_ff, width] */
+    int unary;                 /* UMBS_UNARY_* of a plain part, with its two numbers */
+    float unary_p0, unary_p1;
 } umbs_mlp_t;
 
-typedef struct {
+typedef struct umbs_layer_s {
     int mixer;                 /* UMBS_MIX_* */
     int heads, dim, vdim;
     /* retention */
@@ -178,6 +190,36 @@ typedef struct {
      * row holds [latent | rotated shared part], kv_rank + rope_dim numbers. */
     int rope_dim;
     const float* sink;         /* fp32 [heads] or NULL: with UMBS_ATTN_SOFTMAX_SINK the denominator also holds exp(sink[h]) (NULL: 1) */
+    /* UMBS_NORM_DYT: the scalars of norm_w and norm2_w */
+    float norm_alpha, norm2_alpha;
+    /* cached attention, further options (see umbs_attn_opts_t and umbs_attention_finish) */
+    float softcap;             /* > 0: score <- cap tanh(score / cap), after the scale */
+    const float* dist_r1;      /* fp32 [heads] or NULL: score -= r1[h] ln(1 + r2[h] (i - j)) */
+    const float* dist_r2;
+    const float* talk;         /* fp32 [heads, heads] or NULL: after the softmax head h's weights become sum_g talk[h, g] weights_g;
+                                * the mixed weights meet the values of h's own key/value head */
+    int chunk;                 /* > 0: row i sees key j only if i / chunk == j / chunk (positions from the sequence's start) */
+    int maps;                  /* 0 / 1: one softmax per head; 2: two, [map 1 | map 2] of dim numbers per query and key head over
+                                * the same values, combined as a1 - diff_lambda a2 */
+    float diff_lambda;
+    int head_unit_norm;        /* every head's output is divided by its root mean square (eps inside the root) ... */
+    float out_mult;            /* ... and multiplied by this (0 reads as 1) */
+    const float* q_norm_w;     /* fp32 [dim] or NULL: RMS norm of every query head (and map) with this weight */
+    const float* k_norm_w;     /* fp32 [dim] or NULL: the same for the keys, before they are cached */
+    int kv_from;               /* 0: own keys and values; j + 1: this layer has no key / value rows in w_in and reads layer j's
+                                * step rows and cache (kv_cache, kv_len must be layer j's) */
+    /* time mix (uses heads, dim (= vdim), w_in = [r | k | v | g] rows (4 heads dim), w_o, shift_state, out_norm_w) */
+    const float* mix_mu;       /* fp32 [5, width]: mix s = h + (h_prev - h) mu_s for s = r, k, v, g, w */
+    int decay_rank;
+    const void* w_decay1;      /* [decay_rank, width] */
+    const void* w_decay2;      /* [heads dim, decay_rank] */
+    const float* decay_bias;   /* fp32 [heads dim]: w = exp(-exp(W_2 tanh(W_1 mix_w) + decay_bias)) */
+    const float* bonus;        /* fp32 [heads dim]: weight of the current token's own k v^T in its read-out */
+    float* tm_state;           /* fp32 [slots, heads, dim, dim] */
+    /* a second mixer beside the first: both read the same normed input, the layer adds
+     * mix_scale * first + second_scale * second.  Only its mixer fields are read (no norms, no feed-forward). */
+    const struct umbs_layer_s* second;
+    float mix_scale, second_scale;      /* 0 reads as 1 */
 } umbs_layer_t;
 
 typedef struct {
@@ -193,6 +235,9 @@ typedef struct {
     float embed_scale;         /* the embedding row is multiplied by it (0 reads as 1) */
     int norm_kind;             /* UMBS_NORM_* of the final norm (pre-norm form) */
     const float* final_norm_b; /* fp32 [width]: bias of a final layer norm */
+    float final_norm_alpha;    /* UMBS_NORM_DYT */
+    const float* pos_freq;     /* fp32 [width / 2] or NULL: sinusoidal positions are added to the embedding,
+                                * entry 2i += sin(position pos_freq[i]), entry 2i + 1 += cos(position pos_freq[i]) */
 } umbs_model_t;
 
 const char* umbs_version(void);
@@ -335,8 +380,8 @@ int umbs_depth_mix(const float* x, const float* mix, const float* pair_out, cons
 int umbs_add_rms_norm(int dtype, float* x, const float* delta, const int32_t* rows, int n, const float* w, float w_offset,
                       int width, float eps, void* y, float* copy, umbs_stream_t stream);
 
-/* A block's output waiting to be added to the residual stream: (delta + sum_k sel_w[t, k] pair_out[pair_pos[t, k]] +
- * shared[t] shared_gate[t]) * scale * mult.  Every pointer may be NULL (shared_gate NULL: 1; scale NULL: 1). */
+/* A block's output waiting to be added to the residual stream: (delta_mult delta + delta2_mult delta2 +
+ * sum_k sel_w[t, k] pair_out[pair_pos[t, k]] + shared[t] shared_gate[t]) * scale * mult.  Every pointer may be NULL (shared_gate NULL: 1; scale NULL: 1). */
 typedef struct {
     const float* delta;        /* fp32 [n, width] */
     const float* pair_out;     /* fp32 [n top, width]: the routed experts' outputs in sorted-pair order */
@@ -347,6 +392,9 @@ typedef struct {
     const float* shared_gate;  /* fp32 [n] */
     const float* scale;        /* fp32 [width] */
     float mult;
+    float delta_mult;          /* factor on delta alone (0 reads as 1) */
+    const float* delta2;       /* fp32 [n, width] or NULL: a second dense part, added as delta2_mult * delta2 */
+    float delta2_mult;
 } umbs_delta_t;
 
 /* umbs_add_rms_norm for any pending output and either norm: x[t] += pending(t) (d may be NULL), copy, and
@@ -354,6 +402,11 @@ typedef struct {
  * x[rows[r]] + pending(rows[r]); x is not written.  width <= 8192. */
 int umbs_add_norm(int dtype, float* x, const umbs_delta_t* d, const int32_t* rows, int n, int kind, const float* w,
                   const float* b, float w_offset, int width, float eps, void* y, float* copy, umbs_stream_t stream);
+
+/* umbs_add_norm with the scalar of UMBS_NORM_DYT: y = tanh(alpha x) (w_offset + w) + b. */
+int umbs_add_norm_ex(int dtype, float* x, const umbs_delta_t* d, const int32_t* rows, int n, int kind, const float* w,
+                     const float* b, float w_offset, float alpha, int width, float eps, void* y, float* copy,
+                     umbs_stream_t stream);
 
 /* z <- cap tanh(z / cap), fp32, n values. */
 int umbs_softcap(float* z, int64_t n, float cap, umbs_stream_t stream);
@@ -402,6 +455,76 @@ int umbs_cached_attention(int dtype, int mode, const void* q, const void* kv, co
 int umbs_mlstm(int dtype, const float* proj, int64_t ld, const float* gate_bias, const umbs_batch_t* batch, int heads,
                int dim, int vdim, float gate_cap, float eps, const float* out_norm_w, float* state, float* gates_scratch,
                float* o_scratch, float* seg_scratch, size_t seg_bytes, void* out, umbs_stream_t stream);
+
+/* ---- score options of cached attention, the time-mix memory, and what comes with them ---- */
+
+/* umbs_attention_prep for query and key heads that hold `maps` maps of dim numbers each ([map 1 | map 2 | ...] per head; the
+ * values stay kv_heads vdim) and an RMS norm of every (head, map) over its dim numbers with the weights q_norm_w / k_norm_w
+ * (fp32 [dim], NULL: none; after the convolution, before the rotation; eps inside the root).  kv_heads == 0: the layer
+ * borrows its keys and values, proj holds the query rows only and kv is not written. */
+int umbs_attention_prep_ex(int dtype, const float* proj, int64_t ld, const float* bias, const umbs_batch_t* batch, int heads,
+                           int kv_heads, int dim, int vdim, int values_are_keys, int taps, const float* conv_w,
+                           float* conv_state, int slots, int rot_dims, const float* inv_freq, float rot_mag, int maps,
+                           const float* q_norm_w, const float* k_norm_w, float eps, void* q, void* kv, umbs_stream_t stream);
+
+/* Options of umbs_cached_attention_ex.  With maps = M and value_heads = C the kernel runs heads M C independent softmax rows
+ * per token, numbered (h M + m) C + c: queries (h M + m) dim of q [n_tokens, heads M dim], keys ((h / rep) M + m) dim of a
+ * key/value row [kv_heads M dim | kv_heads vdim], values of head c (C = kv_heads: every query head against every value
+ * head, what talking heads need) or of the query's own key/value head (C = 1). */
+typedef struct {
+    float softcap;             /* > 0: score <- cap tanh(score / cap) after the scale */
+    const float* dist_r1;      /* fp32 [heads] or NULL: score -= r1[h] ln(1 + r2[h] (i - j)) */
+    const float* dist_r2;
+    int chunk;                 /* > 0: key j is visible to row i only if i / chunk == j / chunk */
+    int maps;                  /* 0 reads as 1 */
+    int value_heads;           /* 0 reads as 1 */
+    float* raw_out;            /* fp32 [n_tokens, heads M C, vdim] or NULL: the normalised outputs go here (no gate) instead of out */
+} umbs_attn_opts_t;
+
+/* umbs_cached_attention with umbs_attn_opts_t (NULL: none).  Pooled blocks go with none of the options. */
+int umbs_cached_attention_ex(int dtype, int mode, const void* q, const void* kv, const void* kv_cache, int kv_len,
+                             const void* pool_cache, int pool_len, const umbs_batch_t* batch, int heads, int kv_heads, int dim,
+                             int vdim, int window, int pool, float scale, const float* head_bias, const float* gate,
+                             int64_t ldg, int gate_per_head, const umbs_attn_opts_t* opts, float* split_scratch,
+                             size_t split_bytes, void* out, umbs_stream_t stream);
+
+/* From raw attention outputs (fp32 [n_tokens, heads M C, vdim], see umbs_attn_opts_t) to the mixer's output (`dtype`
+ * [n_tokens, heads vdim]).  talk (fp32 [heads, heads], needs M = 1, C = kv_heads): o_h = sum_g talk[h, g] raw[g, h / rep];
+ * M = 2 (needs C = 1): o_h = raw[h, 0] - diff_lambda raw[h, 1]; unit_norm: o_h / sqrt(mean(o_h^2) + eps); times out_mult;
+ * gate (fp32, or NULL): times sigmoid(gate[t ldg + h vdim + c]).  vdim <= 256. */
+int umbs_attention_finish(int dtype, const float* raw, int n_tokens, int heads, int kv_heads, int vdim, int maps,
+                          int value_heads, const float* talk, float diff_lambda, int unit_norm, float eps, float out_mult,
+                          const float* gate, int64_t ldg, void* out, umbs_stream_t stream);
+
+/* Token-shifted mixes: out[t, s, :] = h[t] + (h[t - 1] - h[t]) mu[s, :], s < n_mix (`dtype` [n_tokens, n_mix, width]); the
+ * row before a sequence's first token of the step comes from shift_state (fp32 [2, slots, width], the half seq_parity names;
+ * zeros at position 0), the step's last row goes to the other half. */
+int umbs_shift_mix(int dtype, const void* h, const float* mu, int n_mix, float* shift_state, int slots,
+                   const umbs_batch_t* batch, int width, void* out, umbs_stream_t stream);
+
+/* The time-mix memory.  proj: fp32 [n_tokens, ld] = [r | k | v | g], heads dim each; decay_raw: fp32 [n_tokens, heads dim].
+ * Per head, with w_t = exp(-exp(decay_raw_t + decay_bias)): o_t = (S + diag(bonus) k_t v_t^T)^T r_t, then
+ * S <- diag(w_t) S + k_t v_t^T (S: dim x dim, key index first; fp32 [slots, heads, dim, dim], read as zero at position 0).
+ * Then o / sqrt(mean(o^2) + eps) per head, times out_norm_w, times silu(g) -> out (`dtype` [n_tokens, heads dim]).
+ * o_scratch: fp32 [n_tokens, heads dim].  dim <= 128. */
+int umbs_time_mix(int dtype, const float* proj, int64_t ld, const float* decay_raw, const float* decay_bias,
+                  const float* bonus, const umbs_batch_t* batch, int heads, int dim, float eps, const float* out_norm_w,
+                  float* state, float* o_scratch, void* out, umbs_stream_t stream);
+
+/* umbs_gemm_ex for a plain product followed by a unary activation (UMBS_UNARY_*, with its two numbers). */
+int umbs_gemm_unary(int dtype, const void* A, int64_t lda, int a_goff, const void* W, int64_t ldw, int64_t w_gstride, void* C,
+                    int64_t ldc, int c_goff, int c_f32, int M, int N, int K, int groups, const float* bias, int unary,
+                    float p0, float p1, umbs_stream_t stream);
+
+/* umbs_moe_route_ex with a factor on the chosen weights; mode may also be UMBS_ROUTE_SOFTMAX_ALL. */
+int umbs_moe_route_scaled(int dtype, const void* h, int n, int width, const float* w_router, int experts, int top, int mode,
+                          int groups, int keep, float weight_scale, float* sel_w, int32_t* grp_off, int32_t* pair_tok,
+                          int32_t* pair_pos, int32_t* scratch, const float* gate_w, float* gate_out, umbs_stream_t stream);
+
+/* y[t] = table[ids[t]] * scale + sinusoidal positions (pos_freq fp32 [width / 2] or NULL: none): entry 2i gets
+ * sin(tok_pos[t] pos_freq[i]), entry 2i + 1 the cosine; angles and sums in fp32. */
+int umbs_embedding_pos(int dtype, const int32_t* ids, const int32_t* tok_pos, const void* table, float scale,
+                       const float* pos_freq, float* y, int n, int width, umbs_stream_t stream);
 
 int umbs_embedding(int dtype, const int32_t* ids, const void* table, float* y, int n, int width, umbs_stream_t stream);
 /* y[t] = table[ids[t]] * scale (fp32). */

@@ -15,7 +15,13 @@ Every live sequence owns one slot.  A slot holds, per layer,
     with pooled blocks a table of one mean key | value row per block, [capacity / pool, .]; with a short convolution
     the last taps - 1 projected q | k rows, fp32, double-buffered like the shift state;
   * mLSTM layers: per head the matrix S with the normaliser n as one more column and the running maximum m,
-    fp32 [heads, dim (vdim + 1) + 1].
+    fp32 [heads, dim (vdim + 1) + 1];
+  * time-mix layers: per head the matrix memory, fp32 [heads, dim, dim] (key index first), and the previous token's
+    normed activations in the token-shift state.
+A cached-attention layer with several maps per head keeps [kv_heads (maps dim + vdim)] numbers per token; one with a
+chunked mask needs a ring of one chunk only; one that borrows another layer's keys and values keeps nothing.  A layer's
+second mixer (two mixers side by side) has state of its own, kept behind the layers' in the same lists
+(``spec.layers[i].second.state_index``).
 and on the host its position (tokens fed so far) and parity.  Nothing is cleared when a slot is freed or handed out
 again: the kernels read a sequence's state as zero while its position is 0, and a ring row is only ever read for a
 position that the current owner has written.
@@ -33,16 +39,27 @@ class SequenceStateCache:
         self.slots = 0
         # tokens per sequence that the growing parts (windowless key/value rows, pooled-block tables) hold
         self.capacity = int(max_length or capacity or 512)
-        self._growing = any((l.mixer == "cached_attention" and (l.window <= 0 or l.pool > 0)) or
-                            (l.mixer == "latent_attention" and l.window <= 0) for l in spec.layers)
-        n = len(spec.layers)
+        # every mixer that keeps state: the layers' own, then the second mixers of layers that run two side by side
+        self.units = []
+        for i, l in enumerate(spec.layers):
+            l.state_index = i
+            self.units.append(l)
+        for l in spec.layers:
+            if getattr(l, "second", None) is not None:
+                l.second.state_index = len(self.units)
+                self.units.append(l.second)
+        self._growing = any((l.mixer == "cached_attention" and l.kv_from is None and
+                             ((l.window <= 0 and l.chunk <= 0) or l.pool > 0)) or
+                            (l.mixer == "latent_attention" and l.window <= 0) for l in self.units)
+        n = len(self.units)
         self.kv_cache: list[torch.Tensor | None] = [None] * n
         self.pool_cache: list[torch.Tensor | None] = [None] * n
         self.conv_state: list[torch.Tensor | None] = [None] * n
         self.mlstm_state: list[torch.Tensor | None] = [None] * n
-        self.shift: list[torch.Tensor | None] = [None] * len(spec.layers)
-        self.ret_state: list[torch.Tensor | None] = [None] * len(spec.layers)
-        self.ring: list[torch.Tensor | None] = [None] * len(spec.layers)
+        self.tm_state: list[torch.Tensor | None] = [None] * n
+        self.shift: list[torch.Tensor | None] = [None] * n
+        self.ret_state: list[torch.Tensor | None] = [None] * n
+        self.ring: list[torch.Tensor | None] = [None] * n
         self.position: list[int] = []
         self.parity: list[int] = []
         self._free: list[int] = []
@@ -57,8 +74,10 @@ class SequenceStateCache:
         return max(1, min(n, self.max_length) if self.max_length else n)
 
     def kv_len(self, layer) -> int:
-        """Rows of a cached-attention layer's key/value cache per slot."""
-        return max(int(layer.window), int(layer.pool), 1) if layer.window > 0 else self.capacity
+        """Rows of a cached-attention layer's key/value cache per slot: the furthest key a row can see -- its window, or
+        its chunk -- bounds the ring; without either, a row per token."""
+        reach = [int(n) for n in (layer.window, layer.chunk) if n > 0]
+        return max(min(reach), int(layer.pool), 1) if reach else self.capacity
 
     def pool_len(self, layer) -> int:
         return max(1, -(-self.capacity // int(layer.pool))) if layer.pool > 0 else 0
@@ -93,21 +112,23 @@ class SequenceStateCache:
                 part.copy_(t_old)
             return t
         self.capacity = capacity
-        for i, l in enumerate(self.spec.layers):
-            if l.shift:
+        for i, l in enumerate(self.units):
+            if l.shift or l.mixer == "time_mix":
                 self.shift[i] = widen(self.shift[i], (2, slots, self.spec.width), 1, **f32)
             if l.mixer == "retention":
                 self.ret_state[i] = widen(self.ret_state[i], (slots, l.heads, l.dim, l.vdim), 0, **f32)
             elif l.mixer == "latent_attention":
                 self.ring[i] = widen(self.ring[i], (slots, self.ring_len(l), l.kv_rank + getattr(l, "rope_dim", 0)), 0,
                                      dtype=self.dtype, device=self.device)
-            elif l.mixer == "cached_attention":
-                row = l.kv_heads * (l.dim + l.vdim)
+            elif l.mixer == "time_mix":
+                self.tm_state[i] = widen(self.tm_state[i], (slots, l.heads, l.dim, l.dim), 0, **f32)
+            elif l.mixer == "cached_attention" and l.kv_from is None:
+                row = l.kv_heads * (l.maps * l.dim + l.vdim)
                 self.kv_cache[i] = widen(self.kv_cache[i], (slots, self.kv_len(l), row), 0, **act)
                 if l.pool > 0:
                     self.pool_cache[i] = widen(self.pool_cache[i], (slots, self.pool_len(l), row), 0, **act)
                 if l.taps > 1:
-                    self.conv_state[i] = widen(self.conv_state[i], (2, slots, l.taps - 1, (l.heads + l.kv_heads) * l.dim),
+                    self.conv_state[i] = widen(self.conv_state[i], (2, slots, l.taps - 1, (l.heads + l.kv_heads) * l.maps * l.dim),
                                                1, **f32)
             elif l.mixer == "mlstm":
                 self.mlstm_state[i] = widen(self.mlstm_state[i], (slots, l.heads, l.dim * (l.vdim + 1) + 1), 0, **f32)
@@ -141,7 +162,8 @@ class SequenceStateCache:
 
     def state_bytes_per_slot(self) -> int:
         n = 0
-        for t in self.shift + self.ret_state + self.ring + self.kv_cache + self.pool_cache + self.conv_state + self.mlstm_state:
+        for t in self.shift + self.ret_state + self.ring + self.kv_cache + self.pool_cache + self.conv_state + self.mlstm_state + \
+                self.tm_state:
             if t is not None:
                 n += t.numel() * t.element_size() // self.slots
         return n

@@ -22,7 +22,7 @@ SOURCES = ["api.cu", "tree.cu", "glue.cu", "attn.cu", "gemm.cu", "forward.cu", "
 HEADERS = ["common.cuh", "internal.h", os.path.join("..", "..", "include", "umbrella_b200.h")]
 SEQ_LIB = os.path.join(HERE, "libumbrella_b200_seq.so")
 SEQ_SOURCES = [os.path.join("seq", f) for f in ("seq_kernels.cu", "seq_window_attn.cu", "seq_gemm.cu", "seq_forward.cu",
-                                                      "seq_prenorm.cu", "seq_cached_attn.cu", "seq_mlstm.cu")]
+                                                      "seq_prenorm.cu", "seq_cached_attn.cu", "seq_mlstm.cu", "seq_timemix.cu")]
 SEQ_HEADERS = [os.path.join("seq", "seq_internal.h"), os.path.join("..", "..", "include", "umbrella_b200.h"),
                os.path.join("..", "..", "include", "umbrella_b200_seq.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -3,6 +3,7 @@
 #include <atomic>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <vector>
 
 #include "seq_internal.h"
 
@@ -55,24 +56,48 @@ struct Scratch {
     float* ca_part;    // fp32 key-split partial sums of cached attention in decode steps
     size_t ca_part_bytes;
     float* sgate;      // fp32 [T]  the shared expert's factor per token
+    float* raw;        // fp32 [T, max heads maps value_heads vdim]  attention outputs in front of umbs_attention_finish
+    void* mixes;       // act [T, 5, width]  token-shifted mixes of a time-mix layer
+    void* lowrank;     // act [T, max decay_rank]
+    float* wraw;       // fp32 [T, max heads dim]  the decay before its exponentials
+    float* mix_out2;   // fp32 [T, width]  a second mixer's output
+    std::vector<void*> kv_rows;   // per layer: the step's key | value rows (a buffer of its own for a layer others borrow from)
 };
+
+// layer j lends its keys and values to a later layer
+static bool lends_kv(const umbs_model_t* m, int j) {
+    for (int i = j + 1; i < m->n_layers; ++i) {
+        if (m->layers[i].kv_from == j + 1) return true;
+        if (m->layers[i].second != nullptr && m->layers[i].second->kv_from == j + 1) return true;
+    }
+    return false;
+}
 
 static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratch* s) {
     const size_t es = m->dtype == UMBS_F32 ? 4 : 2;
     size_t segb = 0;
     int hmax = 1, rotd = 1, in_rows = 1, hv = 1, qr = 1, kvr = 1, hd = 1, hkv = 1, hkvw = 1, top = 1, experts = 1, ff = 1, sff = 1;
-    int hall = 1, cav = 1;
-    bool parallel = false;
-    for (int i = 0; i < m->n_layers; ++i) {
-        const umbs_layer_t& l = m->layers[i];
-        auto up = [](int& a, int b) { if (b > a) a = b; };
+    int hall = 1, cav = 1, rawd = 1, n_mix = 0, rank = 1, tmhd = 1;
+    bool parallel = false, two = false;
+    auto up = [](int& a, int b) { if (b > a) a = b; };
+    for (int i = 0; i < m->n_layers; ++i)
+        if (m->layers[i].form == UMBS_FORM_PARALLEL) parallel = true;
+    for (int u = 0; u < 2 * m->n_layers; ++u) {            // every layer's mixer, then its second one
+        const int i = u >> 1;
+        if ((u & 1) && m->layers[i].second == nullptr) continue;
+        const umbs_layer_t& l = (u & 1) ? *m->layers[i].second : m->layers[i];
+        if (u & 1) two = true;
         up(hv, l.heads * l.vdim);
         up(hall, l.heads);
-        if (l.form == UMBS_FORM_PARALLEL) parallel = true;
         if (l.mixer == UMBS_MIX_CACHED_ATTENTION) {
             const int gate_rows = l.gate_kind == 1 ? l.heads : (l.gate_kind == 2 ? l.heads * l.vdim : 0);
-            up(in_rows, l.heads * l.dim + l.kv_heads * l.dim + (l.values_are_keys ? 0 : l.kv_heads * l.vdim) + gate_rows);
-            up(hd, l.heads * l.dim); up(hkvw, l.kv_heads * (l.dim + l.vdim)); up(cav, l.vdim);
+            const int M = l.maps > 1 ? l.maps : 1;
+            up(in_rows, l.heads * M * l.dim + l.kv_heads * M * l.dim + (l.values_are_keys ? 0 : l.kv_heads * l.vdim) + gate_rows);
+            up(hd, l.heads * M * l.dim); up(hkvw, l.kv_heads * (M * l.dim + l.vdim)); up(cav, l.vdim);
+            up(rawd, l.heads * M * (l.talk != nullptr ? l.kv_heads : 1) * l.vdim);
+        } else if (l.mixer == UMBS_MIX_TIME_MIX) {
+            up(in_rows, 4 * l.heads * l.dim); up(rank, l.decay_rank); up(tmhd, l.heads * l.dim);
+            n_mix = 5;
         } else if (l.mixer == UMBS_MIX_MLSTM) {
             up(in_rows, 2 * l.heads * l.dim + 2 * l.heads * l.vdim + 2 * l.heads);
             up(hv, l.heads * (l.vdim + 1));                        // o32 holds n . q as one more column per head
@@ -93,7 +118,7 @@ static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratc
             up(hkv, l.heads * (l.kv_rank + l.rope_dim));
             if (l.w_ukv != nullptr) up(hkvw, l.heads * (l.dim + l.rope_dim + l.vdim));
         }
-        if (l.has_mlp) { up(top, l.mlp.top); up(experts, l.mlp.experts); up(ff, l.mlp.ff); up(sff, l.mlp.shared_ff); }
+        if (!(u & 1) && l.has_mlp) { up(top, l.mlp.top); up(experts, l.mlp.experts); up(ff, l.mlp.ff); up(sff, l.mlp.shared_ff); }
     }
     Arena a{base, 0, 0};
     const size_t W = m->width, Tz = T;
@@ -131,6 +156,17 @@ static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratc
     z.ca_part_bytes = (size_t)2048 * ((size_t)cav + 2) * 4;                 // (token, head, split) triples of a decode step
     z.ca_part = (float*)a.take(z.ca_part_bytes);
     z.sgate = (float*)a.take(Tz * 4);
+    z.raw = (float*)a.take(Tz * rawd * 4);
+    z.mixes = a.take(Tz * n_mix * W * es);
+    z.lowrank = a.take(Tz * rank * es);
+    z.wraw = (float*)a.take(Tz * tmhd * 4);
+    z.mix_out2 = (float*)a.take(two ? Tz * W * 4 : 0);
+    z.kv_rows.assign(m->n_layers, z.kv);
+    for (int i = 0; i < m->n_layers; ++i) {
+        const umbs_layer_t& l = m->layers[i];
+        if (l.mixer == UMBS_MIX_CACHED_ATTENTION && lends_kv(m, i))
+            z.kv_rows[i] = a.take(Tz * l.kv_heads * ((l.maps > 1 ? l.maps : 1) * l.dim + l.vdim) * es);
+    }
     if (s) *s = z;
     return a.used + 256;
 }
@@ -157,7 +193,8 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
     Scratch s;
     if (carve(m, T, b->n_want, (char*)workspace, &s) > workspace_bytes) return UMB_ERR_WORKSPACE;
     const int64_t plane = (int64_t)T * W;
-    UMBS_TRY(umbs_embedding_scaled(dt, b->tok_ids, m->embed, m->embed_scale != 0.f ? m->embed_scale : 1.f, s.stack, T, W, stream));
+    UMBS_TRY(umbs_embedding_pos(dt, b->tok_ids, b->tok_pos, m->embed, m->embed_scale != 0.f ? m->embed_scale : 1.f, m->pos_freq,
+                                s.stack, T, W, stream));
     const float* x = s.stack;                    // layer 0 reads X_0 itself
     bool prenorm = false;
     for (int i = 0; i < m->n_layers; ++i) {
@@ -169,34 +206,94 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
     umbs_delta_t pend{};
     bool has_pend = false;
     // the residual add + norm in front of a block: the plain RMS kernel where nothing else is asked for
-    auto norm_step = [&](const int32_t* rows, int n, int kind, const float* w, const float* bias, float off, void* y,
-                         float* copy) -> int {
+    auto norm_step = [&](const int32_t* rows, int n, int kind, const float* w, const float* bias, float off, float alpha,
+                         void* y, float* copy) -> int {
         const bool plain = kind == UMBS_NORM_RMS && (!has_pend || (pend.pair_out == nullptr && pend.shared == nullptr &&
-                                                                   pend.scale == nullptr && pend.mult == 1.f));
+                                                                   pend.scale == nullptr && pend.mult == 1.f &&
+                                                                   pend.delta2 == nullptr && (pend.delta_mult == 0.f || pend.delta_mult == 1.f)));
         if (plain) return umbs_add_rms_norm(dt, s.stack, has_pend ? pend.delta : nullptr, rows, n, w, off, W, m->norm_eps, y, copy, stream);
-        return umbs_add_norm(dt, s.stack, has_pend ? &pend : nullptr, rows, n, kind, w, bias, off, W, m->norm_eps, y, copy, stream);
+        return umbs_add_norm_ex(dt, s.stack, has_pend ? &pend : nullptr, rows, n, kind, w, bias, off, alpha, W, m->norm_eps, y, copy,
+                                stream);
+    };
+    // One mixer of a pre-norm layer: from the normed rows s.h to its output, fp32 [T, width] at `out`.  li: the layer's index.
+    auto run_mixer = [&](const umbs_layer_t& l, int li, float* out) -> int {
+        const int hv = l.heads * l.vdim;
+        if (l.mixer == UMBS_MIX_CACHED_ATTENTION) {
+            const int M = l.maps > 1 ? l.maps : 1;
+            const bool borrowed = l.kv_from > 0;
+            const int src = borrowed ? l.kv_from - 1 : li;
+            if (borrowed && (src >= li || m->layers[src].mixer != UMBS_MIX_CACHED_ATTENTION || m->layers[src].kv_from > 0 ||
+                             l.values_are_keys || l.taps > 1 || l.pool > 0))
+                return UMB_ERR_UNSUPPORTED;
+            const int cq = l.heads * M * l.dim, ck = borrowed ? 0 : l.kv_heads * M * l.dim;
+            const int cv = (borrowed || l.values_are_keys) ? 0 : l.kv_heads * l.vdim;
+            const int gate_rows = l.gate_kind == 1 ? l.heads : (l.gate_kind == 2 ? hv : 0);
+            const int rows = cq + ck + cv + gate_rows, row_kv = l.kv_heads * (M * l.dim + l.vdim);
+            void* kv_rows = s.kv_rows[src];
+            const float* gate = gate_rows ? s.proj + cq + ck + cv : nullptr;
+            UMBS_TRY(umbs_gemm(dt, s.h, W, 0, l.w_in, W, 0, s.proj, rows, 0, 1, T, rows, W, 1, nullptr, nullptr, 0, 0.f, stream));
+            UMBS_TRY(umbs_attention_prep_ex(dt, s.proj, rows, l.bias_in, b, l.heads, borrowed ? 0 : l.kv_heads, l.dim, l.vdim,
+                                            l.values_are_keys, l.taps, l.conv_w, l.conv_state, m->slots, l.rot_dims, l.inv_freq,
+                                            l.rot_mag, M, l.q_norm_w, l.k_norm_w, m->norm_eps, s.q, borrowed ? nullptr : kv_rows,
+                                            stream));
+            if (l.pool > 0)
+                UMBS_TRY(umbs_kv_pool(dt, kv_rows, l.kv_cache, l.kv_len, l.pool_cache, l.pool_len, b, row_kv, l.pool, stream));
+            const bool finish = l.talk != nullptr || M > 1 || l.head_unit_norm || (l.out_mult != 0.f && l.out_mult != 1.f);
+            if (finish && l.gate_kind == 1) return UMB_ERR_UNSUPPORTED;
+            umbs_attn_opts_t opts{};
+            opts.softcap = l.softcap; opts.dist_r1 = l.dist_r1; opts.dist_r2 = l.dist_r2; opts.chunk = l.chunk; opts.maps = M;
+            opts.value_heads = l.talk != nullptr ? l.kv_heads : 1;
+            opts.raw_out = finish ? s.raw : nullptr;
+            UMBS_TRY(umbs_cached_attention_ex(dt, l.attn_mode, s.q, kv_rows, l.kv_cache, l.kv_len, l.pool_cache, l.pool_len, b,
+                                              l.heads, l.kv_heads, l.dim, l.vdim, l.window, l.pool, l.scale, l.head_bias,
+                                              finish ? nullptr : gate, rows, l.gate_kind == 1, &opts, s.ca_part, s.ca_part_bytes,
+                                              s.mixed, stream));
+            if (finish)
+                UMBS_TRY(umbs_attention_finish(dt, s.raw, T, l.heads, l.kv_heads, l.vdim, M, opts.value_heads, l.talk, l.diff_lambda,
+                                               l.head_unit_norm, m->norm_eps, l.out_mult, gate, rows, s.mixed, stream));
+            if (!borrowed && !lends_kv(m, li))           // (a lender's rows go to its cache after its last borrower has run)
+                UMBS_TRY(umbs_ring_append(dt, kv_rows, l.kv_cache, l.kv_len, b, row_kv, stream));
+        } else if (l.mixer == UMBS_MIX_TIME_MIX) {
+            const int hd = l.heads * l.dim, rows = 4 * hd;
+            const size_t es = dt == UMBS_F32 ? 4 : 2;
+            if (l.vdim != l.dim || l.mix_mu == nullptr || l.shift_state == nullptr || l.decay_rank < 1) return UMB_ERR_ARG;
+            UMBS_TRY(umbs_shift_mix(dt, s.h, l.mix_mu, 5, l.shift_state, m->slots, b, W, s.mixes, stream));
+            // r | k | v | g: one batched product over the first four mixes
+            UMBS_TRY(umbs_gemm(dt, s.mixes, (int64_t)5 * W, W, l.w_in, W, (int64_t)hd * W, s.proj, rows, hd, 1, T, hd, W, 4, nullptr,
+                               nullptr, 0, 0.f, stream));
+            // the decay's low-rank map of the fifth mix, tanh in the first product's epilogue
+            UMBS_TRY(umbs_gemm_unary(dt, (const char*)s.mixes + (size_t)4 * W * es, (int64_t)5 * W, 0, l.w_decay1, W, 0, s.lowrank,
+                                     l.decay_rank, 0, 0, T, l.decay_rank, W, 1, nullptr, UMBS_UNARY_TANH, 0.f, 0.f, stream));
+            UMBS_TRY(umbs_gemm(dt, s.lowrank, l.decay_rank, 0, l.w_decay2, l.decay_rank, 0, s.wraw, hd, 0, 1, T, hd, l.decay_rank, 1,
+                               nullptr, nullptr, 0, 0.f, stream));
+            UMBS_TRY(umbs_time_mix(dt, s.proj, rows, s.wraw, l.decay_bias, l.bonus, b, l.heads, l.dim, m->norm_eps, l.out_norm_w,
+                                   l.tm_state, s.o32, s.mixed, stream));
+        } else {
+            return UMB_ERR_UNSUPPORTED;
+        }
+        return umbs_gemm(dt, s.mixed, hv, 0, l.w_o, hv, 0, out, W, 0, 1, T, W, hv, 1, nullptr, nullptr, 0, 0.f, stream);
     };
     for (int i = 0; prenorm && i < m->n_layers; ++i) {
         const umbs_layer_t& l = m->layers[i];
         const int hv = l.heads * l.vdim;
         const float mult = l.residual_mult != 0.f ? l.residual_mult : 1.f;
-        UMBS_TRY(norm_step(nullptr, T, l.norm_kind, l.norm_w, l.norm_b, l.norm_offset, s.h,
+        UMBS_TRY(norm_step(nullptr, T, l.norm_kind, l.norm_w, l.norm_b, l.norm_offset, l.norm_alpha, s.h,
                            (layer_out && i > 0) ? layer_out + (int64_t)(i - 1) * plane : nullptr));
-        if (l.mixer == UMBS_MIX_CACHED_ATTENTION) {
-            const int cq = l.heads * l.dim, ck = l.kv_heads * l.dim, cv = l.values_are_keys ? 0 : l.kv_heads * l.vdim;
-            const int gate_rows = l.gate_kind == 1 ? l.heads : (l.gate_kind == 2 ? hv : 0);
-            const int rows = cq + ck + cv + gate_rows, row_kv = l.kv_heads * (l.dim + l.vdim);
-            UMBS_TRY(umbs_gemm(dt, s.h, W, 0, l.w_in, W, 0, s.proj, rows, 0, 1, T, rows, W, 1, nullptr, nullptr, 0, 0.f, stream));
-            UMBS_TRY(umbs_attention_prep(dt, s.proj, rows, l.bias_in, b, l.heads, l.kv_heads, l.dim, l.vdim, l.values_are_keys,
-                                         l.taps, l.conv_w, l.conv_state, m->slots, l.rot_dims, l.inv_freq, l.rot_mag, s.q, s.kv,
-                                         stream));
-            if (l.pool > 0)
-                UMBS_TRY(umbs_kv_pool(dt, s.kv, l.kv_cache, l.kv_len, l.pool_cache, l.pool_len, b, row_kv, l.pool, stream));
-            UMBS_TRY(umbs_cached_attention(dt, l.attn_mode, s.q, s.kv, l.kv_cache, l.kv_len, l.pool_cache, l.pool_len, b, l.heads,
-                                           l.kv_heads, l.dim, l.vdim, l.window, l.pool, l.scale, l.head_bias,
-                                           gate_rows ? s.proj + cq + ck + cv : nullptr, rows, l.gate_kind == 1, s.ca_part,
-                                           s.ca_part_bytes, s.mixed, stream));
-            UMBS_TRY(umbs_ring_append(dt, s.kv, l.kv_cache, l.kv_len, b, row_kv, stream));
+        const bool generic = l.mixer == UMBS_MIX_CACHED_ATTENTION || l.mixer == UMBS_MIX_TIME_MIX;
+        if (generic) {
+            UMBS_TRY(run_mixer(l, i, s.mix_out));
+            if (l.second != nullptr) UMBS_TRY(run_mixer(*l.second, i, s.mix_out2));
+            // rows a layer lent out go to its cache once its last borrower has run
+            for (int j = 0; j <= i; ++j) {
+                const umbs_layer_t& lj = m->layers[j];
+                if (lj.mixer != UMBS_MIX_CACHED_ATTENTION || lj.kv_from > 0 || !lends_kv(m, j)) continue;
+                int last = j;
+                for (int k = j + 1; k < m->n_layers; ++k)
+                    if (m->layers[k].kv_from == j + 1 || (m->layers[k].second && m->layers[k].second->kv_from == j + 1)) last = k;
+                if (last == i)
+                    UMBS_TRY(umbs_ring_append(dt, s.kv_rows[j], lj.kv_cache, lj.kv_len, b,
+                                              lj.kv_heads * ((lj.maps > 1 ? lj.maps : 1) * lj.dim + lj.vdim), stream));
+            }
         } else if (l.mixer == UMBS_MIX_MLSTM) {
             const int rows = 2 * l.heads * l.dim + 2 * hv + 2 * l.heads;
             UMBS_TRY(umbs_gemm(dt, s.h, W, 0, l.w_in, W, 0, s.proj, rows, 0, 1, T, rows, W, 1, nullptr, nullptr, 0, 0.f, stream));
@@ -237,22 +334,27 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
         } else {
             return UMB_ERR_UNSUPPORTED;
         }
-        UMBS_TRY(umbs_gemm(dt, s.mixed, hv, 0, l.w_o, hv, 0, s.mix_out, W, 0, 1, T, W, hv, 1, nullptr, nullptr, 0, 0.f, stream));
+        if (!generic) {
+            if (l.second != nullptr) return UMB_ERR_UNSUPPORTED;
+            UMBS_TRY(umbs_gemm(dt, s.mixed, hv, 0, l.w_o, hv, 0, s.mix_out, W, 0, 1, T, W, hv, 1, nullptr, nullptr, 0, 0.f, stream));
+        }
         pend = umbs_delta_t{};
         pend.delta = s.mix_out; pend.scale = l.out_scale; pend.mult = mult;
+        pend.delta_mult = l.mix_scale != 0.f ? l.mix_scale : 1.f;
+        if (l.second != nullptr) { pend.delta2 = s.mix_out2; pend.delta2_mult = l.second_scale != 0.f ? l.second_scale : 1.f; }
         has_pend = true;
         if (l.has_mlp) {
             const umbs_mlp_t& f = l.mlp;
             if ((f.experts <= 0 && f.shared_ff <= 0) || l.norm2_w == nullptr) return UMB_ERR_UNSUPPORTED;
             const int act = f.act ? f.act : UMBS_ACT_CLAMPED_GLU;
-            UMBS_TRY(norm_step(nullptr, T, l.norm_kind, l.norm2_w, l.norm2_b, l.norm_offset, s.h, nullptr));
+            UMBS_TRY(norm_step(nullptr, T, l.norm_kind, l.norm2_w, l.norm2_b, l.norm_offset, l.norm2_alpha, s.h, nullptr));
             pend = umbs_delta_t{};
             pend.scale = l.out_scale2; pend.mult = mult;
             if (f.experts > 0) {
                 // (the shared expert's per-token gate rides along as one more row of the router)
-                UMBS_TRY(umbs_moe_route_ex(dt, s.h, T, W, f.w_router, f.experts, f.top, f.route_mode, f.groups, f.keep, s.sel_w,
-                                           s.grp_off, s.pair_tok, s.pair_pos, s.route_scratch,
-                                           f.shared_ff > 0 ? f.w_shared_gate : nullptr, s.sgate, stream));
+                UMBS_TRY(umbs_moe_route_scaled(dt, s.h, T, W, f.w_router, f.experts, f.top, f.route_mode, f.groups, f.keep,
+                                               f.route_scale, s.sel_w, s.grp_off, s.pair_tok, s.pair_pos, s.route_scratch,
+                                               f.shared_ff > 0 ? f.w_shared_gate : nullptr, s.sgate, stream));
                 UMBS_TRY(umbs_gemm(dt, s.h, W, 0, f.w_gu, W, (int64_t)2 * f.ff * W, s.y, f.ff, 0, 0, T, f.ff, W, f.experts,
                                    s.grp_off, s.pair_tok, act, f.limit, stream));
                 UMBS_TRY(umbs_gemm(dt, s.y, f.ff, 0, f.w_down, f.ff, (int64_t)W * f.ff, s.pair_out, W, 0, 1, T, W, f.ff, f.experts,
@@ -260,6 +362,10 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
                 pend.pair_out = s.pair_out; pend.sel_w = s.sel_w; pend.pair_pos = s.pair_pos; pend.top = f.top;
             }
             if (f.shared_ff > 0) {
+                if (f.plain)           // no gate rows: the activation of the up product alone, in its epilogue
+                    UMBS_TRY(umbs_gemm_unary(dt, s.h, W, 0, f.ws_gu, W, 0, s.ys, f.shared_ff, 0, 0, T, f.shared_ff, W, 1, f.bias_gu,
+                                             f.unary, f.unary_p0, f.unary_p1, stream));
+                else
                 UMBS_TRY(umbs_gemm_ex(dt, s.h, W, 0, f.ws_gu, W, 0, s.ys, f.shared_ff, 0, 0, T, f.shared_ff, W, 1, nullptr, nullptr,
                                       act, f.shared_limit, f.bias_gu, nullptr, 0, 0, stream));
                 UMBS_TRY(umbs_gemm_ex(dt, s.ys, f.shared_ff, 0, f.ws_down, f.shared_ff, 0, s.shared_out, W, 0, 1, T, W, f.shared_ff, 1,
@@ -276,12 +382,12 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
     }
     if (prenorm) {
         if (layer_out != nullptr) {              // the last layer's stream is asked for: finish the sum for every row
-            UMBS_TRY(norm_step(nullptr, T, UMBS_NORM_RMS, nullptr, nullptr, 0.f, nullptr, layer_out + (int64_t)(m->n_layers - 1) * plane));
+            UMBS_TRY(norm_step(nullptr, T, UMBS_NORM_RMS, nullptr, nullptr, 0.f, 1.f, nullptr, layer_out + (int64_t)(m->n_layers - 1) * plane));
             has_pend = false;
         }
         if (logits != nullptr && b->n_want > 0) {
-            UMBS_TRY(norm_step(b->want_rows, b->n_want, m->norm_kind, m->final_norm, m->final_norm_b, m->norm_offset, s.final_h,
-                               nullptr));
+            UMBS_TRY(norm_step(b->want_rows, b->n_want, m->norm_kind, m->final_norm, m->final_norm_b, m->norm_offset,
+                               m->final_norm_alpha, s.final_h, nullptr));
             UMBS_TRY(umbs_gemm(dt, s.final_h, W, 0, m->head, W, 0, logits, m->vocab, 0, 1, b->n_want, m->vocab, W, 1, nullptr,
                                nullptr, 0, 0.f, stream));
             if (m->logit_softcap > 0.f) UMBS_TRY(umbs_softcap(logits, (int64_t)b->n_want * m->vocab, m->logit_softcap, stream));

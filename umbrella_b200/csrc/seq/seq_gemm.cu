@@ -31,7 +31,15 @@ struct GemmArgs {
     const float* out_gate;   // fp32: the result is multiplied by sigmoid(out_gate[row ld_gate + g gate_goff + n]), or NULL
     int64_t ld_gate;
     int gate_goff;
+    int unary;        // UMBS_UNARY_* of a plain product, with its two numbers
+    float p0, p1;
 };
+
+__device__ __forceinline__ float unary_act(float z, int unary, float p0, float p1) {
+    if (unary == UMBS_UNARY_TANH) return tanhf(z);
+    if (unary == UMBS_UNARY_XIELU) return z > 0.f ? fmaf(p0 * z, z, 0.5f * z) : fmaf(p1, expm1f(z) - z, 0.5f * z);
+    return z;
+}
 
 __device__ __forceinline__ float gated_act(float g, float u, float limit, int act) {
     if (act == UMBS_ACT_GELU_TANH) {      // 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))) * u
@@ -51,7 +59,7 @@ __device__ __forceinline__ float finish(const GemmArgs& a, float s, float s2, in
         s += a.bias[n];
         if (DUAL) s2 += a.bias[a.N + n];
     }
-    float v = DUAL ? gated_act(s, s2, a.limit, a.act) : s;
+    float v = DUAL ? gated_act(s, s2, a.limit, a.act) : (a.unary ? unary_act(s, a.unary, a.p0, a.p1) : s);
     if (a.out_gate != nullptr) v *= 1.f / (1.f + expf(-a.out_gate[row * a.ld_gate + (int64_t)g * a.gate_goff + n]));
     return v;
 }
@@ -349,6 +357,11 @@ static void launch_mma(const GemmArgs& a, int groups, bool dual, cudaStream_t st
 
 using namespace umbs;
 
+static int gemm_run(int dtype, const void* A, int64_t lda, int a_goff, const void* W, int64_t ldw, int64_t w_gstride,
+                    void* C, int64_t ldc, int c_goff, int c_f32, int M, int N, int K, int groups,
+                    const int32_t* grp_off, const int32_t* row_src, int dual, float limit, const float* bias,
+                    const float* out_gate, int64_t ld_gate, int gate_goff, int unary, float p0, float p1, umbs_stream_t stream);
+
 extern "C" int umbs_gemm(int dtype, const void* A, int64_t lda, int a_goff, const void* W, int64_t ldw, int64_t w_gstride,
                          void* C, int64_t ldc, int c_goff, int c_f32, int M, int N, int K, int groups,
                          const int32_t* grp_off, const int32_t* row_src, int dual, float limit, umbs_stream_t stream) {
@@ -360,12 +373,28 @@ extern "C" int umbs_gemm_ex(int dtype, const void* A, int64_t lda, int a_goff, c
                             void* C, int64_t ldc, int c_goff, int c_f32, int M, int N, int K, int groups,
                             const int32_t* grp_off, const int32_t* row_src, int dual, float limit, const float* bias,
                             const float* out_gate, int64_t ld_gate, int gate_goff, umbs_stream_t stream) {
+    return gemm_run(dtype, A, lda, a_goff, W, ldw, w_gstride, C, ldc, c_goff, c_f32, M, N, K, groups, grp_off, row_src, dual, limit,
+                    bias, out_gate, ld_gate, gate_goff, 0, 0.f, 0.f, stream);
+}
+
+extern "C" int umbs_gemm_unary(int dtype, const void* A, int64_t lda, int a_goff, const void* W, int64_t ldw, int64_t w_gstride,
+                               void* C, int64_t ldc, int c_goff, int c_f32, int M, int N, int K, int groups, const float* bias,
+                               int unary, float p0, float p1, umbs_stream_t stream) {
+    if (unary != 0 && unary != UMBS_UNARY_TANH && unary != UMBS_UNARY_XIELU) return UMB_ERR_ARG;
+    return gemm_run(dtype, A, lda, a_goff, W, ldw, w_gstride, C, ldc, c_goff, c_f32, M, N, K, groups, nullptr, nullptr, 0, 0.f, bias,
+                    nullptr, 0, 0, unary, p0, p1, stream);
+}
+
+static int gemm_run(int dtype, const void* A, int64_t lda, int a_goff, const void* W, int64_t ldw, int64_t w_gstride,
+                    void* C, int64_t ldc, int c_goff, int c_f32, int M, int N, int K, int groups,
+                    const int32_t* grp_off, const int32_t* row_src, int dual, float limit, const float* bias,
+                    const float* out_gate, int64_t ld_gate, int gate_goff, int unary, float p0, float p1, umbs_stream_t stream) {
     if (M <= 0 || N <= 0 || groups <= 0) return 0;
     if (K <= 0 || A == nullptr || W == nullptr || C == nullptr) return UMB_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     GemmArgs a{A, lda, a_goff, W, ldw, w_gstride, C, ldc, c_goff, M, N, K, grp_off, row_src, limit,
                (dual == UMBS_ACT_GELU_TANH || dual == UMBS_ACT_SILU) ? dual : UMBS_ACT_CLAMPED_GLU,
-               bias, out_gate, ld_gate, gate_goff};
+               bias, out_gate, ld_gate, gate_goff, unary, p0, p1};
     if (dtype == UMBS_F32) {
         launch_simt<float, float>(a, groups, dual != 0, st);          // activations are fp32 too: c_f32 changes nothing
     } else if (dtype == UMBS_BF16) {

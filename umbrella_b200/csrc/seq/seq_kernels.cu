@@ -39,12 +39,21 @@ __device__ float block_sum(float v, float* red) {   // red: >= 33 floats of shar
 }
 
 // ------------------------------------------------------------------------------------------------ embedding
+// (pos_freq != NULL: sinusoidal positions on top -- sine at the even entries, cosine at the odd ones, one frequency per pair)
 template <typename T>
 __global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table, float* __restrict__ y,
-                                 int width, float scale) {
+                                 int width, float scale, const int32_t* __restrict__ tok_pos, const float* __restrict__ pos_freq) {
     const int t = blockIdx.x;
     const T* row = table + (int64_t)ids[t] * width;
-    for (int e = threadIdx.x; e < width; e += blockDim.x) y[(int64_t)t * width + e] = to_f32(row[e]) * scale;
+    const float pos = pos_freq != nullptr ? (float)tok_pos[t] : 0.f;
+    for (int e = threadIdx.x; e < width; e += blockDim.x) {
+        float v = to_f32(row[e]) * scale;
+        if (pos_freq != nullptr && (e >> 1) < width / 2) {
+            const float ang = pos * pos_freq[e >> 1];
+            v += (e & 1) ? cosf(ang) : sinf(ang);
+        }
+        y[(int64_t)t * width + e] = v;
+    }
 }
 
 // ------------------------------------------------------------------------------------------------ group norm (+ shift)
@@ -573,7 +582,9 @@ __device__ __forceinline__ float router_logit(const T* __restrict__ hr, const fl
 // `top` rounds of arg-max over z (lowest index wins a tie; z is consumed) and the softmax over the chosen logits.
 // UMBS_ROUTE_SIGMOID_GROUPS: z becomes sigmoid(z); a group's score is the sum of its two largest scores; `keep` rounds of
 // arg-max over the groups mark the eligible ones; `top` rounds of arg-max over the eligible scores; weights = score / sum.
-__device__ __forceinline__ void route_choose(float* z, int experts, int top, int mode, int groups, int keep,
+// UMBS_ROUTE_SOFTMAX_ALL: the softmax's sum runs over every expert, the chosen scores are not renormalised.
+// Every weight is multiplied by wscale at the end.
+__device__ __forceinline__ void route_choose(float* z, int experts, int top, int mode, int groups, int keep, float wscale,
                                              float* __restrict__ w_out, int32_t* __restrict__ e_out, int32_t* counts) {
     if (mode == UMBS_ROUTE_SIGMOID_GROUPS) {
         const int per = experts / groups;
@@ -607,30 +618,35 @@ __device__ __forceinline__ void route_choose(float* z, int experts, int top, int
             z[best] = -INFINITY;
             atomicAdd(counts + best, 1);
         }
-        for (int k = 0; k < top; ++k) w_out[k] /= (den + 1e-20f);
+        for (int k = 0; k < top; ++k) w_out[k] = w_out[k] / (den + 1e-20f) * wscale;
         return;
     }
     float zmax = 0.f, den = 0.f;
+    if (mode == UMBS_ROUTE_SOFTMAX_ALL) {
+        zmax = -INFINITY;
+        for (int e = 0; e < experts; ++e) zmax = fmaxf(zmax, z[e]);
+        for (int e = 0; e < experts; ++e) den += expf(z[e] - zmax);
+    }
     for (int k = 0; k < top; ++k) {
         int best = 0;
         float bv = -INFINITY;
         for (int e = 0; e < experts; ++e)
             if (z[e] > bv) { bv = z[e]; best = e; }
-        if (k == 0) zmax = bv;
+        if (k == 0 && mode != UMBS_ROUTE_SOFTMAX_ALL) zmax = bv;
         const float p = expf(bv - zmax);
         e_out[k] = best;
         w_out[k] = p;
-        den += p;
+        if (mode != UMBS_ROUTE_SOFTMAX_ALL) den += p;
         z[best] = -INFINITY;
         atomicAdd(counts + best, 1);
     }
-    for (int k = 0; k < top; ++k) w_out[k] /= den;
+    for (int k = 0; k < top; ++k) w_out[k] = w_out[k] / den * wscale;
 }
 
 // One block per token: the warps share the experts' logits, then one thread chooses.
 template <typename T>
 __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ h, int n, int width, const float* __restrict__ wr,
-                                                         int experts, int top, int mode, int groups, int keep,
+                                                         int experts, int top, int mode, int groups, int keep, float wscale,
                                                          float* __restrict__ sel_w, int32_t* __restrict__ sel_e,
                                                          int32_t* __restrict__ counts, const float* __restrict__ gate_w,
                                                          float* __restrict__ gate_out) {
@@ -648,7 +664,7 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ h
     }
     __syncthreads();
     if (threadIdx.x == 0)
-        route_choose(z, experts, top, mode, groups, keep, sel_w + (int64_t)t * top, sel_e + (int64_t)t * top, counts);
+        route_choose(z, experts, top, mode, groups, keep, wscale, sel_w + (int64_t)t * top, sel_e + (int64_t)t * top, counts);
 }
 
 // The whole routing of a small step (a decode step) in one block: logits of every (token, expert) pair, the choice per
@@ -657,7 +673,7 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ h
 template <typename T>
 __global__ void __launch_bounds__(1024) moe_route_small_kernel(const T* __restrict__ h, int n, int width,
                                                               const float* __restrict__ wr, int experts, int top,
-                                                              int mode, int groups, int keep,
+                                                              int mode, int groups, int keep, float wscale,
                                                               float* __restrict__ sel_w, int32_t* __restrict__ sel_e,
                                                               int32_t* __restrict__ grp_off, int32_t* __restrict__ pair_tok,
                                                               int32_t* __restrict__ pair_pos, const float* __restrict__ gate_w,
@@ -679,7 +695,7 @@ __global__ void __launch_bounds__(1024) moe_route_small_kernel(const T* __restri
     }
     __syncthreads();
     for (int t = threadIdx.x; t < n; t += blockDim.x)
-        route_choose(zs + t * experts, experts, top, mode, groups, keep, sel_w + (int64_t)t * top, chosen + t * top, counts);
+        route_choose(zs + t * experts, experts, top, mode, groups, keep, wscale, sel_w + (int64_t)t * top, chosen + t * top, counts);
     __syncthreads();
     if (threadIdx.x == 0) {
         int s = 0;
@@ -777,9 +793,16 @@ extern "C" int umbs_embedding(int dtype, const int32_t* ids, const void* table, 
 
 extern "C" int umbs_embedding_scaled(int dtype, const int32_t* ids, const void* table, float scale, float* y, int n, int width,
                                      umbs_stream_t stream) {
+    return umbs_embedding_pos(dtype, ids, nullptr, table, scale, nullptr, y, n, width, stream);
+}
+
+extern "C" int umbs_embedding_pos(int dtype, const int32_t* ids, const int32_t* tok_pos, const void* table, float scale,
+                                  const float* pos_freq, float* y, int n, int width, umbs_stream_t stream) {
     if (n <= 0) return 0;
+    if (pos_freq != nullptr && tok_pos == nullptr) return UMB_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
-    UMBS_DISPATCH_T(dtype, embedding_kernel<T><<<n, threads_for(width), 0, st>>>(ids, (const T*)table, y, width, scale));
+    UMBS_DISPATCH_T(dtype, embedding_kernel<T><<<n, threads_for(width), 0, st>>>(ids, (const T*)table, y, width, scale, tok_pos,
+                                                                              pos_freq));
     count_launches(1);
     return (int)cudaGetLastError();
 }
@@ -999,12 +1022,21 @@ extern "C" int umbs_moe_route_ex(int dtype, const void* h, int n, int width, con
                                  int mode, int groups, int keep, float* sel_w, int32_t* grp_off, int32_t* pair_tok,
                                  int32_t* pair_pos, int32_t* scratch, const float* gate_w, float* gate_out,
                                  umbs_stream_t stream) {
+    return umbs_moe_route_scaled(dtype, h, n, width, w_router, experts, top, mode, groups, keep, 1.f, sel_w, grp_off, pair_tok,
+                                 pair_pos, scratch, gate_w, gate_out, stream);
+}
+
+extern "C" int umbs_moe_route_scaled(int dtype, const void* h, int n, int width, const float* w_router, int experts, int top,
+                                     int mode, int groups, int keep, float weight_scale, float* sel_w, int32_t* grp_off,
+                                     int32_t* pair_tok, int32_t* pair_pos, int32_t* scratch, const float* gate_w,
+                                     float* gate_out, umbs_stream_t stream) {
     if (n <= 0) return 0;
+    if (weight_scale == 0.f) weight_scale = 1.f;
     if (top < 1 || top > experts || (gate_w != nullptr && gate_out == nullptr)) return UMB_ERR_ARG;
     if (mode == UMBS_ROUTE_SIGMOID_GROUPS) {
         if (groups < 1 || experts % groups != 0 || keep < 1 || keep > groups || top > keep * (experts / groups)) return UMB_ERR_ARG;
         if (groups > 64) return UMB_ERR_UNSUPPORTED;
-    } else if (mode != UMBS_ROUTE_SOFTMAX_TOP) {
+    } else if (mode != UMBS_ROUTE_SOFTMAX_TOP && mode != UMBS_ROUTE_SOFTMAX_ALL) {
         return UMB_ERR_ARG;
     }
     cudaStream_t st = (cudaStream_t)stream;
@@ -1012,7 +1044,7 @@ extern "C" int umbs_moe_route_ex(int dtype, const void* h, int n, int width, con
         // a small step (decoding): one block does the logits, the choice, the offsets and the sorted pair list
         const size_t smem = ((size_t)n * experts + 2 * (size_t)experts + 1 + (size_t)n * top) * sizeof(float);
         UMBS_DISPATCH_T(dtype, moe_route_small_kernel<T><<<1, 1024, smem, st>>>((const T*)h, n, width, w_router, experts, top,
-                                                                              mode, groups, keep, sel_w, scratch + 2 * experts,
+                                                                              mode, groups, keep, weight_scale, sel_w, scratch + 2 * experts,
                                                                               grp_off, pair_tok, pair_pos, gate_w, gate_out));
         count_launches(1);
         return (int)cudaGetLastError();
@@ -1024,8 +1056,8 @@ extern "C" int umbs_moe_route_ex(int dtype, const void* h, int n, int width, con
     if (e != cudaSuccess) return (int)e;
     const int rthreads = experts >= 8 ? 256 : 32 * experts;
     UMBS_DISPATCH_T(dtype, moe_router_kernel<T><<<n, rthreads, (size_t)experts * sizeof(float), st>>>(
-                               (const T*)h, n, width, w_router, experts, top, mode, groups, keep, sel_w, sel_e, counts, gate_w,
-                               gate_out));
+                               (const T*)h, n, width, w_router, experts, top, mode, groups, keep, weight_scale, sel_w, sel_e, counts,
+                               gate_w, gate_out));
     moe_offsets_kernel<<<1, 32, 0, st>>>(counts, experts, grp_off, cursor);
     const int pairs = n * top;
     moe_scatter_kernel<<<(pairs + 255) / 256, 256, 0, st>>>(sel_e, pairs, top, grp_off, cursor, pair_tok, pair_pos);

@@ -96,8 +96,8 @@ __device__ __forceinline__ float block_sum_pn(float v, float* red) {
 
 template <typename T>
 __global__ void add_norm_kernel(float* __restrict__ x, umbs_delta_t d, int has_d, const int32_t* __restrict__ rows, int kind,
-                                const float* __restrict__ w, const float* __restrict__ bias, float w_offset, int width, float eps,
-                                T* __restrict__ y, float* __restrict__ copy) {
+                                const float* __restrict__ w, const float* __restrict__ bias, float w_offset, float alpha, int width,
+                                float eps, T* __restrict__ y, float* __restrict__ copy) {
     __shared__ float red[33];
     constexpr int KEEP = 8, TOPS = 16;              // up to TOPS routed pairs per token are held in shared memory
     __shared__ float s_w[TOPS];
@@ -135,7 +135,8 @@ __global__ void add_norm_kernel(float* __restrict__ x, umbs_delta_t d, int has_d
         if (e < width) {
             float dl = 0.f;
             if (has_d) {
-                if (d.delta != nullptr) dl = d.delta[src * width + e];
+                if (d.delta != nullptr) dl = d.delta[src * width + e] * d.delta_mult;
+                if (d.delta2 != nullptr) dl = fmaf(d.delta2[src * width + e], d.delta2_mult, dl);
                 dl += ff[i];
                 if (d.shared != nullptr) dl = fmaf(d.shared[src * width + e], sg, dl);
                 if (d.scale != nullptr) dl *= d.scale[e];
@@ -146,7 +147,7 @@ __global__ void add_norm_kernel(float* __restrict__ x, umbs_delta_t d, int has_d
         }
     }
     float mean = 0.f, inv = 0.f;
-    if (y != nullptr) {
+    if (y != nullptr && kind != UMBS_NORM_DYT) {          // (the tanh norm takes no statistics)
         sum = block_sum_pn(sum, red);
         if (kind == UMBS_NORM_LAYER) {
             mean = sum / (float)width;
@@ -166,8 +167,8 @@ __global__ void add_norm_kernel(float* __restrict__ x, umbs_delta_t d, int has_d
             if (write_x) xr[e] = v[i];
             if (copy != nullptr) copy[(int64_t)r * width + e] = v[i];
             if (y != nullptr) {
-                float o = (v[i] - mean) * inv * (w_offset + w[e]);
-                if (kind == UMBS_NORM_LAYER && bias != nullptr) o += bias[e];
+                float o = kind == UMBS_NORM_DYT ? tanhf(alpha * v[i]) * (w_offset + w[e]) : (v[i] - mean) * inv * (w_offset + w[e]);
+                if (kind != UMBS_NORM_RMS && bias != nullptr) o += bias[e];
                 y[(int64_t)r * width + e] = from_f32<T>(o);
             }
         }
@@ -226,10 +227,11 @@ template <typename T>
 __global__ void attention_prep_kernel(const float* __restrict__ proj, int64_t ld, const float* __restrict__ bias, Batch b,
                                       int heads, int kv_heads, int dim, int vdim, int values_are_keys, int taps,
                                       const float* __restrict__ conv_w, float* __restrict__ conv_state, int slots, int rot_dims,
-                                      const float* __restrict__ inv_freq, float rot_mag, T* __restrict__ q_out,
-                                      T* __restrict__ kv_out) {
+                                      const float* __restrict__ inv_freq, float rot_mag, int maps,
+                                      const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
+                                      T* __restrict__ q_out, T* __restrict__ kv_out) {
     extern __shared__ float sm[];                 // [heads dim + kv_heads dim] convolved q | k, then cos | sin [rot_dims]
-    const int Cq = heads * dim, Ck = kv_heads * dim, C = Cq + Ck, Cv = kv_heads * vdim;
+    const int Cq = heads * maps * dim, Ck = kv_heads * maps * dim, C = Cq + Ck, Cv = kv_heads * vdim;
     float* y = sm;
     float* cs = sm + C;
     const int t = blockIdx.x, s = b.tok_seq[t], pos = b.tok_pos[t];
@@ -269,6 +271,21 @@ __global__ void attention_prep_kernel(const float* __restrict__ proj, int64_t ld
         }
     }
     __syncthreads();
+    if (q_norm_w != nullptr || k_norm_w != nullptr) {
+        // RMS norm of every (head, map): a warp per group of dim channels, lanes striding over it
+        const int lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+        for (int grp = threadIdx.x >> 5; grp < C / dim; grp += nw) {
+            const float* nwt = grp * dim < Cq ? q_norm_w : k_norm_w;
+            if (nwt == nullptr) continue;
+            float* yg = y + grp * dim;
+            float ss = 0.f;
+            for (int d = lane; d < dim; d += 32) ss = fmaf(yg[d], yg[d], ss);
+            ss = warp_sum_pn(ss);
+            const float inv = 1.f / sqrtf(ss / (float)dim + eps);
+            for (int d = lane; d < dim; d += 32) yg[d] = yg[d] * inv * nwt[d];
+        }
+        __syncthreads();
+    }
     const int row_kv = Ck + Cv;
     T* qo = q_out + (int64_t)t * Cq;
     T* ko = kv_out + (int64_t)t * row_kv;
@@ -286,7 +303,7 @@ __global__ void attention_prep_kernel(const float* __restrict__ proj, int64_t ld
             if (values_are_keys) ko[Ck + (c - Cq)] = from_f32<T>(y[c]);
         }
     }
-    if (!values_are_keys)
+    if (!values_are_keys && kv_out != nullptr)
         for (int c = threadIdx.x; c < Cv; c += blockDim.x) ko[Ck + c] = from_f32<T>(row[C + c] + (bias ? bias[C + c] : 0.f));
 }
 
@@ -342,9 +359,15 @@ extern "C" int umbs_add_rms_norm(int dtype, float* x, const float* delta, const 
 
 extern "C" int umbs_add_norm(int dtype, float* x, const umbs_delta_t* d, const int32_t* rows, int n, int kind, const float* w,
                              const float* b, float w_offset, int width, float eps, void* y, float* copy, umbs_stream_t stream) {
+    return umbs_add_norm_ex(dtype, x, d, rows, n, kind, w, b, w_offset, 1.f, width, eps, y, copy, stream);
+}
+
+extern "C" int umbs_add_norm_ex(int dtype, float* x, const umbs_delta_t* d, const int32_t* rows, int n, int kind, const float* w,
+                                const float* b, float w_offset, float alpha, int width, float eps, void* y, float* copy,
+                                umbs_stream_t stream) {
     if (n <= 0) return 0;
     if (x == nullptr || width <= 0 || (y != nullptr && w == nullptr)) return UMB_ERR_ARG;
-    if (kind != UMBS_NORM_RMS && kind != UMBS_NORM_LAYER) return UMB_ERR_ARG;
+    if (kind != UMBS_NORM_RMS && kind != UMBS_NORM_LAYER && kind != UMBS_NORM_DYT) return UMB_ERR_ARG;
     if (width > 8192) return UMB_ERR_UNSUPPORTED;                 // a row lives in the block's registers
     if (d != nullptr && d->pair_out != nullptr && (d->sel_w == nullptr || d->pair_pos == nullptr || d->top < 1)) return UMB_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
@@ -352,8 +375,9 @@ extern "C" int umbs_add_norm(int dtype, float* x, const umbs_delta_t* d, const i
     if (threads < 64) threads = 64;
     umbs_delta_t dd{};
     if (d != nullptr) dd = *d;
-    UMBS_DISPATCH_T(dtype, add_norm_kernel<T><<<n, threads, 0, st>>>(x, dd, d != nullptr, rows, kind, w, b, w_offset, width, eps,
-                                                                     (T*)y, copy));
+    if (dd.delta_mult == 0.f) dd.delta_mult = 1.f;
+    UMBS_DISPATCH_T(dtype, add_norm_kernel<T><<<n, threads, 0, st>>>(x, dd, d != nullptr, rows, kind, w, b, w_offset, alpha, width,
+                                                                     eps, (T*)y, copy));
     count_launches(1);
     return (int)cudaGetLastError();
 }
@@ -387,19 +411,31 @@ extern "C" int umbs_attention_prep(int dtype, const float* proj, int64_t ld, con
                                    int heads, int kv_heads, int dim, int vdim, int values_are_keys, int taps,
                                    const float* conv_w, float* conv_state, int slots, int rot_dims, const float* inv_freq,
                                    float rot_mag, void* q, void* kv, umbs_stream_t stream) {
+    if (kv_heads < 1) return UMB_ERR_ARG;
+    return umbs_attention_prep_ex(dtype, proj, ld, bias, batch, heads, kv_heads, dim, vdim, values_are_keys, taps, conv_w, conv_state,
+                                  slots, rot_dims, inv_freq, rot_mag, 1, nullptr, nullptr, 0.f, q, kv, stream);
+}
+
+extern "C" int umbs_attention_prep_ex(int dtype, const float* proj, int64_t ld, const float* bias, const umbs_batch_t* batch,
+                                      int heads, int kv_heads, int dim, int vdim, int values_are_keys, int taps,
+                                      const float* conv_w, float* conv_state, int slots, int rot_dims, const float* inv_freq,
+                                      float rot_mag, int maps, const float* q_norm_w, const float* k_norm_w, float eps, void* q,
+                                      void* kv, umbs_stream_t stream) {
     if (batch->n_tokens <= 0) return 0;
-    if (rot_dims < 0 || rot_dims > dim || (rot_dims & 1) || taps < 1 || kv_heads < 1 || heads % kv_heads != 0) return UMB_ERR_ARG;
+    if (maps < 1) maps = 1;
+    if (rot_dims < 0 || rot_dims > dim || (rot_dims & 1) || taps < 1 || kv_heads < 0 || heads < 1) return UMB_ERR_ARG;
+    if (kv_heads > 0 ? (heads % kv_heads != 0 || kv == nullptr) : values_are_keys) return UMB_ERR_ARG;
     if (values_are_keys && vdim != dim) return UMB_ERR_ARG;
     if (taps > 1 && (conv_w == nullptr || conv_state == nullptr)) return UMB_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
-    const int C = (heads + kv_heads) * dim;
+    const int C = (heads + kv_heads) * maps * dim;
     const size_t smem = ((size_t)C + rot_dims + 2) * sizeof(float);
     if (smem > 48 * 1024) return UMB_ERR_UNSUPPORTED;
     // a small step (decoding) has few blocks: spread a token's channels over up to 1024 threads
     const int threads = batch->n_tokens <= 64 ? std::min(1024, (C + 31) / 32 * 32) : (C >= 1024 ? 256 : 128);
     UMBS_DISPATCH_T(dtype, attention_prep_kernel<T><<<batch->n_tokens, threads, smem, st>>>(
                                proj, ld, bias, *batch, heads, kv_heads, dim, vdim, values_are_keys, taps, conv_w, conv_state, slots,
-                               rot_dims, inv_freq, rot_mag, (T*)q, (T*)kv));
+                               rot_dims, inv_freq, rot_mag, maps, q_norm_w, k_norm_w, eps, (T*)q, (T*)kv));
     count_launches(1);
     return (int)cudaGetLastError();
 }

@@ -59,8 +59,13 @@ def _kulisun(path, **kw):
     return kulisun.from_pretrained(path, **kw)
 
 
+def _subivik(path, **kw):
+    from . import subivik
+    return subivik.from_pretrained(path, **kw)
+
+
 # config.json ``architecture`` -> factory(path, device=, dtype=, max_length=, slots=, max_tokens=, ...)
-_ARCHITECTURES = {"Radanex": _radanex, "Zedotar": _zedotar, "Kulisun": _kulisun}
+_ARCHITECTURES = {"Radanex": _radanex, "Zedotar": _zedotar, "Kulisun": _kulisun, "Subivik": _subivik}
 
 
 def _make(model_name, offload=False, batch_size=1, max_length=None, device="cuda:0", dtype=torch.float16, **unused):

@@ -4,7 +4,8 @@ A model is a ``SeqModelSpec``: width, vocabulary, the norm's constants and a lis
 its form (``"parallel"``: one grouped norm feeds mixer and feed-forward side by side, with token shift and a depth
 average as options; ``"prenorm"``: x += mixer(norm1(x)), x += ff(norm2(x)), RMS or layer norms, optionally with a learned
 scale vector and a multiplier on every block's output), its mixer (``"retention"``, ``"latent_attention"``,
-``"cached_attention"`` or ``"mlstm"``) with that mixer's sizes and constants, and its feed-forward (routed experts and /
+``"cached_attention"``, ``"mlstm"`` or ``"time_mix"``) with that mixer's sizes and constants -- a pre-norm layer may run a
+second mixer beside the first (``second``), both reading the same normed rows --, and its feed-forward (routed experts and /
 or a shared expert -- a dense feed-forward is a shared expert alone -- or none).  Model families (models/radanex.py,
 models/zedotar.py, models/kulisun.py) translate their config.json into a spec and their tensors into the per-layer
 weight dicts ``load_layer`` takes; nothing below knows a family's names.
@@ -40,6 +41,9 @@ class SeqMlpSpec:
     keep: int = 1                     # ... of which the best `keep` (by the sum of their two largest scores) stay eligible
     bias: bool = False                # the shared (dense) projections carry biases
     shared_gate: bool = False         # the shared expert's output is multiplied by sigmoid(w . h), a number per token
+    route_scale: float = 1.0          # factor on the chosen experts' weights ("softmax_all": softmax over every expert, the
+                                      # chosen scores as they are)
+    plain: str = ""                   # the dense part has no gate: W_down act(W_up h), act = "xielu" (two learned numbers)
 
 
 @dataclass
@@ -71,17 +75,34 @@ class SeqLayerSpec:
     head_bias: bool = False           # a number per head added to the scores
     inv_freq: list | None = None      # rotary frequencies when they are not base^(-2i/rot_dims) (scaled forms)
     rot_mag: float = 1.0              # factor on cos and sin
+    # cached attention, score options
+    softcap: float = 0.0              # > 0: score <- cap tanh(score / cap)
+    dist_bias: bool = False           # score -= r1[h] ln(1 + r2[h] (i - j)), two learned numbers per head
+    talk: bool = False                # after the softmax, head h's weights become a learned mix of all heads' weights
+    chunk: int = 0                    # > 0: a row sees only keys of its own chunk of this many positions
+    maps: int = 1                     # 2: differential attention, a1 - lambda a2 over the same values
+    diff: float = 0.0                 # lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff; the output is scaled by 1 - diff
+    head_unit_norm: bool = False      # every head's output is divided by its root mean square
+    qk_norm: bool = False             # RMS norm (weight [dim]) of every query and key head (and map)
+    kv_from: int | None = None        # the layer has no key / value projections and reads that layer's keys and values
+    # time mix (dim = vdim)
+    decay_rank: int = 0
+    # a second mixer beside this one (pre-norm form): x += mix_scale * mixer + second_scale * second
+    second: "SeqLayerSpec | None" = None
+    mix_scale: float = 1.0
+    second_scale: float = 1.0
     # mlstm
     gate_cap: float = 0.0
     # layer
     form: str = "parallel"
     norm_offset: float = 0.0          # added to the layer's norm weights (1: weights stored around zero)
-    norm_kind: str = "rms"            # pre-norm form: "rms" | "layer" (mean removed, weight and bias)
+    norm_kind: str = "rms"            # pre-norm form: "rms" | "layer" (mean removed, weight and bias) | "dyt" (tanh(alpha x) w + b)
     layer_scale: bool = False         # pre-norm form: every block's output is multiplied by a learned vector
     residual_mult: float = 1.0        # pre-norm form: x += residual_mult * block output
     shift: bool = True
     depth_average: bool = True
     mlp: SeqMlpSpec | None = None
+    state_index: int = -1             # where the state cache keeps this mixer's state (set by the cache)
 
 
 @dataclass
@@ -95,6 +116,8 @@ class SeqModelSpec:
     logit_softcap: float = 0.0        # > 0: logits <- cap tanh(logits / cap)
     embed_scale: float = 1.0          # factor on the embedding rows
     norm_kind: str = "rms"            # kind of the final norm (pre-norm form)
+    pos_embed: str = ""               # "sinusoid": entry 2i of the embedding gets sin(p f_i), entry 2i + 1 cos(p f_i), ...
+    pos_base: float = 10000.0         # ... f_i = pos_base^(-2i / width)
     eos_token_id: list = field(default_factory=list)
 
     # compatibility with the engines' view of a config
@@ -141,11 +164,16 @@ def rotary_inv_freq64(rot_dims: int, base: float) -> torch.Tensor:
 
 
 _MIXERS = {"retention": S.UMBS_MIX_RETENTION, "latent_attention": S.UMBS_MIX_LATENT_ATTENTION,
-           "cached_attention": S.UMBS_MIX_CACHED_ATTENTION, "mlstm": S.UMBS_MIX_MLSTM}
+           "cached_attention": S.UMBS_MIX_CACHED_ATTENTION, "mlstm": S.UMBS_MIX_MLSTM, "time_mix": S.UMBS_MIX_TIME_MIX}
 _ATTN_MODES = {"softmax": S.UMBS_ATTN_SOFTMAX, "softmax_sink": S.UMBS_ATTN_SOFTMAX_SINK, "sigmoid": S.UMBS_ATTN_SIGMOID}
 _ACTS = {"clamped_glu": S.UMBS_ACT_CLAMPED_GLU, "gelu_tanh": S.UMBS_ACT_GELU_TANH, "silu": S.UMBS_ACT_SILU}
-_NORMS = {"rms": S.UMBS_NORM_RMS, "layer": S.UMBS_NORM_LAYER}
-_ROUTES = {"softmax_top": S.UMBS_ROUTE_SOFTMAX_TOP, "sigmoid_groups": S.UMBS_ROUTE_SIGMOID_GROUPS}
+_NORMS = {"rms": S.UMBS_NORM_RMS, "layer": S.UMBS_NORM_LAYER, "dyt": S.UMBS_NORM_DYT}
+_ROUTES = {"softmax_top": S.UMBS_ROUTE_SOFTMAX_TOP, "sigmoid_groups": S.UMBS_ROUTE_SIGMOID_GROUPS,
+           "softmax_all": S.UMBS_ROUTE_SOFTMAX_ALL}
+
+
+def _softplus(z: float) -> float:
+    return math.log1p(math.exp(-abs(z))) + max(z, 0.0)
 
 
 class SeqStateModel:
@@ -205,11 +233,18 @@ class SeqStateModel:
     def _f32(self, t: torch.Tensor) -> torch.Tensor:
         return t.to(self.device, torch.float32).contiguous()
 
-    def load_head(self, embed: torch.Tensor, head: torch.Tensor, final_norm: torch.Tensor,
-                  final_norm_b: torch.Tensor | None = None):
-        self.head_weights = dict(embed=self._act(embed), head=self._act(head), final_norm=self._f32(final_norm))
-        if self.spec.norm_kind == "layer":
+    def load_head(self, embed: torch.Tensor, head: torch.Tensor | None, final_norm: torch.Tensor,
+                  final_norm_b: torch.Tensor | None = None, final_norm_alpha: float = 1.0):
+        """``head`` None: the logits come from the embedding table itself (tied)."""
+        e = self._act(embed)
+        self.head_weights = dict(embed=e, head=e if head is None else self._act(head), final_norm=self._f32(final_norm))
+        if self.spec.norm_kind in ("layer", "dyt"):
             self.head_weights["final_norm_b"] = self._f32(final_norm_b)
+        self.final_norm_alpha = float(final_norm_alpha)
+        if self.spec.pos_embed == "sinusoid":
+            self.head_weights["pos_freq"] = rotary_inv_freq(self.spec.width, self.spec.pos_base).to(self.device)
+        elif self.spec.pos_embed:
+            raise ValueError(f"unknown position embedding '{self.spec.pos_embed}'")
         self._c_model = None
 
     def load_layer(self, idx: int, w: dict):
@@ -228,15 +263,18 @@ class SeqStateModel:
         feed-forward: router [experts, width]; experts: list of (gate, up, down); shared (or dense): (gate, up, down);
             dense_b: (gate_b, up_b, down_b) with ``bias``; shared_gate [1, width] or [width]."""
         l = self.spec.layers[idx]
-        d = dict(norm=self._f32(w["norm"]), o=self._act(w["o"]))
+        d = dict(norm=self._f32(w["norm"]))
         if l.form == "prenorm":
             l.shift = l.depth_average = False
             if l.mlp is not None:
                 d["norm2"] = self._f32(w["norm2"])
-            if l.norm_kind == "layer":
+            if l.norm_kind in ("layer", "dyt"):
                 d["norm_b"] = self._f32(w["norm_b"])
                 if l.mlp is not None:
                     d["norm2_b"] = self._f32(w["norm2_b"])
+            if l.norm_kind == "dyt":           # the scalars inside the tanh
+                d["norm_alpha"] = float(w["norm_alpha"])
+                d["norm2_alpha"] = float(w["norm2_alpha"]) if l.mlp is not None else 1.0
             if l.layer_scale:
                 d["ls1"] = self._f32(w["ls1"])
                 if l.mlp is not None:
@@ -246,6 +284,20 @@ class SeqStateModel:
         if l.depth_average:
             d["depth"] = self._f32(w["depth"])
             assert d["depth"].numel() == idx + 2
+        self._load_mixer(l, w, d)
+        if l.second is not None:
+            if l.form != "prenorm" or l.mixer not in ("cached_attention", "time_mix") or \
+                    l.second.mixer not in ("cached_attention", "time_mix"):
+                raise ValueError("a second mixer goes with pre-norm layers of cached attention and time mix")
+            d["second"] = {}
+            self._load_mixer(l.second, w["second"], d["second"])
+        self._load_mlp(l, w, d)
+        self.weights[idx] = d
+        self._c_model = None
+
+    def _load_mixer(self, l, w: dict, d: dict):
+        """The mixer's tensors of ``w`` (see load_layer) into ``d``, stacked as the kernels read them."""
+        d["o"] = self._act(w["o"])
         if l.mixer == "retention":
             d["w_in"] = self._act(torch.cat([w["q"], w["k"], w["v"], w["g"]], dim=0))
             d["inv_freq"] = rotary_inv_freq(l.rot_dims, l.rot_base).to(self.device) if l.rot_dims else \
@@ -283,11 +335,29 @@ class SeqStateModel:
             d["ukv"] = self._act(torch.cat([w["uk"], w["uv"]], dim=0))
             assert d["uq"].shape == (l.heads * l.dim, l.q_rank) and d["uv"].shape == (l.heads * l.vdim, l.kv_rank)
         elif l.mixer == "cached_attention":
-            # in-projection rows: q | k | v (unless the values are the keys) | gate; biases for q | k | v in the same order
-            cq, ck = l.heads * l.dim, l.kv_heads * l.dim
-            parts = [w["q"], w["k"]] + ([] if l.values_are_keys else [w["v"]]) + ([w["g"]] if l.gate_kind else [])
+            # in-projection rows: q | k | v (unless the values are the keys) | gate; biases for q | k | v in the same order;
+            # with several maps a head's rows are [map 1 | map 2]; a layer that borrows keys and values has q | gate only
+            cq, ck = l.heads * l.maps * l.dim, l.kv_heads * l.maps * l.dim
+            own = l.kv_from is None
+            parts = [w["q"]] + ([w["k"]] if own else []) + ([] if (l.values_are_keys or not own) else [w["v"]]) + \
+                ([w["g"]] if l.gate_kind else [])
             d["w_in"] = self._act(torch.cat(parts, dim=0))
-            assert w["q"].shape[0] == cq and w["k"].shape[0] == ck and l.heads % l.kv_heads == 0
+            assert w["q"].shape[0] == cq and (not own or w["k"].shape[0] == ck) and l.heads % l.kv_heads == 0
+            assert l.maps in (1, 2) and not (l.talk and l.maps > 1)
+            if l.dist_bias:
+                d["r1"], d["r2"] = self._f32(w["r1"]), self._f32(w["r2"])
+                assert d["r1"].numel() == l.heads and d["r2"].numel() == l.heads
+            if l.talk:
+                d["talk"] = self._f32(w["talk"])
+                assert d["talk"].shape == (l.heads, l.heads)
+            if l.qk_norm:
+                d["q_norm"] = self._f32(w["q_norm"])
+                if own:
+                    d["k_norm"] = self._f32(w["k_norm"])
+                assert d["q_norm"].numel() == l.dim
+            if l.maps == 2:        # one number per layer, from four learned vectors: evaluated once, in double
+                dot = lambda a, b: float((w[a].double() * w[b].double()).sum())
+                d["diff_lambda"] = math.exp(dot("lq1", "lk1")) - math.exp(dot("lq2", "lk2")) + l.diff
             assert not l.gate_kind or w["g"].shape[0] == (l.heads if l.gate_kind == 1 else l.heads * l.vdim)
             assert not l.values_are_keys or l.vdim == l.dim
             if l.bias:
@@ -302,6 +372,16 @@ class SeqStateModel:
             d["inv_freq"] = f.to(torch.float32).to(self.device) if l.rot_dims else \
                 torch.zeros(1, dtype=torch.float32, device=self.device)
             assert l.rot_dims == 0 or d["inv_freq"].numel() == l.rot_dims // 2
+        elif l.mixer == "time_mix":
+            # the four projections that read their own token-shifted mix, stacked for one batched product
+            hd = l.heads * l.dim
+            d["w_in"] = self._act(torch.stack([w["r"], w["k"], w["v"], w["g"]]))
+            d["mu"] = self._f32(torch.stack([w["mu_r"], w["mu_k"], w["mu_v"], w["mu_g"], w["mu_w"]]))
+            d["w1"], d["w2"] = self._act(w["w1"]), self._act(w["w2"])
+            d["w0"], d["u"], d["out_norm"] = self._f32(w["w0"]), self._f32(w["u"].reshape(-1)), self._f32(w["out_norm"])
+            l.decay_rank = int(w["w1"].shape[0])
+            assert l.vdim == l.dim and d["w_in"].shape == (4, hd, self.spec.width) and d["mu"].shape == (5, self.spec.width)
+            assert d["w2"].shape == (hd, l.decay_rank) and d["w0"].numel() == hd and d["u"].numel() == hd and d["out_norm"].numel() == hd
         elif l.mixer == "mlstm":
             d["w_in"] = self._act(torch.cat([w["q"], w["k"], w["v"], w["g"], w["i"], w["f"]], dim=0))
             d["bias_in"] = self._f32(torch.cat([w["i_b"], w["f_b"]]))
@@ -311,8 +391,19 @@ class SeqStateModel:
         else:
             raise ValueError(f"unknown mixer '{l.mixer}'")
         assert d["o"].shape == (self.spec.width, l.heads * l.vdim)
+
+    def _load_mlp(self, l, w: dict, d: dict):
         if l.mlp is not None:
             m = l.mlp
+            if m.plain:
+                if m.plain != "xielu" or m.experts or l.form != "prenorm":
+                    raise ValueError("a plain feed-forward is W_down xielu(W_up h) of a pre-norm layer")
+                up, dn = w["dense"]
+                d["s_gu"], d["s_down"] = self._act(up), self._act(dn)
+                p, q = (float(x) for x in w["dense_act"].double().reshape(-1))
+                d["unary_p"] = (_softplus(p), 0.5 + _softplus(q))        # the two coefficients, evaluated once in double
+                assert d["s_gu"].shape == (m.shared_ff, self.spec.width) and d["s_down"].shape == (self.spec.width, m.shared_ff)
+                return
             if m.experts:
                 d["router"] = self._f32(w["router"])
                 d["gu"] = self._act(torch.stack([torch.cat([g, u], dim=0) for g, u, _ in w["experts"]]))
@@ -329,13 +420,21 @@ class SeqStateModel:
                 if m.shared_gate:
                     d["s_gate"] = self._f32(w["shared_gate"].reshape(-1))
                     assert d["s_gate"].numel() == self.spec.width
-        self.weights[idx] = d
-        self._c_model = None
 
     def weight_bytes(self) -> int:
-        n = sum(t.numel() * t.element_size() for t in self.head_weights.values())
+        seen, n = set(), 0
+
+        def count(d):
+            nonlocal n
+            for t in d.values():
+                if isinstance(t, dict):
+                    count(t)
+                elif isinstance(t, torch.Tensor) and t.data_ptr() not in seen:       # (a tied head counts once)
+                    seen.add(t.data_ptr())
+                    n += t.numel() * t.element_size()
+        count(self.head_weights)
         for d in self.weights:
-            n += sum(t.numel() * t.element_size() for t in d.values())
+            count(d)
         return n
 
     # ------------------------------------------------------------------ C structs
@@ -346,14 +445,12 @@ class SeqStateModel:
         sp, cache = self.spec, self.cache
         p = lambda t: t.data_ptr() if t is not None else None
         layers = (S.Layer * self.num_layers)()
-        for i, (l, w) in enumerate(zip(sp.layers, self.weights)):
-            cl = layers[i]
+        seconds = []
+
+        def fill_mixer(cl, l, w, i):
+            """The mixer's part of a layer struct; i: where the cache keeps this mixer's state."""
             cl.mixer = _MIXERS[l.mixer]
             cl.heads, cl.dim, cl.vdim = l.heads, l.dim, l.vdim
-            cl.form = S.UMBS_FORM_PRENORM if l.form == "prenorm" else S.UMBS_FORM_PARALLEL
-            cl.norm_offset, cl.norm2_w = l.norm_offset, p(w.get("norm2"))
-            cl.norm_kind, cl.norm_b, cl.norm2_b = _NORMS[l.norm_kind], p(w.get("norm_b")), p(w.get("norm2_b"))
-            cl.out_scale, cl.out_scale2, cl.residual_mult = p(w.get("ls1")), p(w.get("ls2")), l.residual_mult
             if l.mixer == "retention":
                 cl.rot_dims, cl.inv_freq, cl.decay = l.rot_dims, p(w["inv_freq"]), p(w["decay"])
                 cl.ret_state = p(cache.ret_state[i])
@@ -362,9 +459,22 @@ class SeqStateModel:
                 cl.values_are_keys, cl.pool, cl.taps, cl.window, cl.scale = int(l.values_are_keys), l.pool, l.taps, l.window, l.scale
                 cl.rot_dims, cl.inv_freq, cl.rot_mag = l.rot_dims, p(w["inv_freq"]), l.rot_mag
                 cl.bias_in, cl.conv_w, cl.head_bias = p(w.get("bias_in")), p(w.get("conv_w")), p(w.get("head_bias"))
-                cl.kv_cache, cl.kv_len = p(cache.kv_cache[i]), cache.kv_len(l)
+                src = sp.layers[l.kv_from] if l.kv_from is not None else l           # whose rows the cache holds
+                if l.kv_from is not None and (src.mixer != "cached_attention" or src.kv_from is not None or
+                                              (src.kv_heads, src.dim, src.vdim, src.maps) != (l.kv_heads, l.dim, l.vdim, l.maps)):
+                    raise ValueError("kv_from must name an earlier cached-attention layer of the same key and value shape")
+                cl.kv_from = 0 if l.kv_from is None else l.kv_from + 1
+                cl.kv_cache, cl.kv_len = p(cache.kv_cache[src.state_index]), cache.kv_len(src)
                 cl.pool_cache, cl.pool_len = p(cache.pool_cache[i]), cache.pool_len(l)
                 cl.conv_state = p(cache.conv_state[i])
+                cl.softcap, cl.dist_r1, cl.dist_r2, cl.talk = l.softcap, p(w.get("r1")), p(w.get("r2")), p(w.get("talk"))
+                cl.chunk, cl.maps, cl.diff_lambda = l.chunk, l.maps, w.get("diff_lambda", 0.0)
+                cl.head_unit_norm, cl.out_mult = int(l.head_unit_norm), (1.0 - l.diff) if l.maps == 2 else 1.0
+                cl.q_norm_w, cl.k_norm_w = p(w.get("q_norm")), p(w.get("k_norm"))
+            elif l.mixer == "time_mix":
+                cl.mix_mu, cl.decay_rank, cl.w_decay1, cl.w_decay2 = p(w["mu"]), l.decay_rank, p(w["w1"]), p(w["w2"])
+                cl.decay_bias, cl.bonus, cl.out_norm_w = p(w["w0"]), p(w["u"]), p(w["out_norm"])
+                cl.tm_state, cl.shift_state = p(cache.tm_state[i]), p(cache.shift[i])
             elif l.mixer == "mlstm":
                 cl.gate_cap, cl.bias_in, cl.out_norm_w = l.gate_cap, p(w["bias_in"]), p(w["out_norm"])
                 cl.mlstm_state = p(cache.mlstm_state[i])
@@ -378,9 +488,25 @@ class SeqStateModel:
                 if l.q_rank == 0:
                     cl.rope_dim, cl.rot_dims, cl.inv_freq, cl.rot_mag = l.rope_dim, l.rot_dims, p(w["inv_freq"]), l.rot_mag
                     cl.attn_mode, cl.gate_kind, cl.sink = _ATTN_MODES[l.attn_mode], l.gate_kind, p(w.get("sink"))
-            cl.w_in, cl.w_o, cl.norm_w = p(w["w_in"]), p(w["o"]), p(w["norm"])
-            cl.shift_w, cl.shift_state = p(w.get("shift")), p(cache.shift[i])
+            cl.w_in, cl.w_o = p(w["w_in"]), p(w["o"])
+
+        for i, (l, w) in enumerate(zip(sp.layers, self.weights)):
+            cl = layers[i]
+            fill_mixer(cl, l, w, i)
+            cl.form = S.UMBS_FORM_PRENORM if l.form == "prenorm" else S.UMBS_FORM_PARALLEL
+            cl.norm_offset, cl.norm2_w = l.norm_offset, p(w.get("norm2"))
+            cl.norm_kind, cl.norm_b, cl.norm2_b = _NORMS[l.norm_kind], p(w.get("norm_b")), p(w.get("norm2_b"))
+            cl.norm_alpha, cl.norm2_alpha = w.get("norm_alpha", 1.0), w.get("norm2_alpha", 1.0)
+            cl.out_scale, cl.out_scale2, cl.residual_mult = p(w.get("ls1")), p(w.get("ls2")), l.residual_mult
+            cl.norm_w = p(w["norm"])
+            if l.mixer != "time_mix":
+                cl.shift_w, cl.shift_state = p(w.get("shift")), p(cache.shift[i])
             cl.depth_w = p(w.get("depth"))
+            if l.second is not None:
+                sec = S.Layer()
+                fill_mixer(sec, l.second, w["second"], l.second.state_index)
+                seconds.append(sec)
+                cl.second, cl.mix_scale, cl.second_scale = C.pointer(sec), l.mix_scale, l.second_scale
             cl.has_mlp = int(l.mlp is not None)
             if l.mlp is not None:
                 m = l.mlp
@@ -392,6 +518,10 @@ class SeqStateModel:
                 cl.mlp.route_mode, cl.mlp.groups, cl.mlp.keep = _ROUTES[m.route], m.groups, m.keep
                 cl.mlp.bias_gu, cl.mlp.bias_down = p(w.get("s_gu_b")), p(w.get("s_down_b"))
                 cl.mlp.w_shared_gate = p(w.get("s_gate"))
+                cl.mlp.route_scale = m.route_scale
+                if m.plain:
+                    cl.mlp.plain, cl.mlp.unary = 1, S.UMBS_UNARY_XIELU
+                    cl.mlp.unary_p0, cl.mlp.unary_p1 = w["unary_p"]
         m = S.Model()
         m.dtype = S.UMBS_BF16 if self.dtype == torch.bfloat16 else S.UMBS_F32
         m.width, m.vocab, m.n_layers, m.norm_groups, m.slots = sp.width, sp.vocab, self.num_layers, sp.norm_groups, cache.slots
@@ -399,8 +529,9 @@ class SeqStateModel:
         hw = self.head_weights
         m.embed, m.final_norm, m.head = p(hw["embed"]), p(hw["final_norm"]), p(hw["head"])
         m.embed_scale, m.norm_kind, m.final_norm_b = sp.embed_scale, _NORMS[sp.norm_kind], p(hw.get("final_norm_b"))
+        m.final_norm_alpha, m.pos_freq = getattr(self, "final_norm_alpha", 1.0), p(hw.get("pos_freq"))
         m.layers = C.cast(layers, C.POINTER(S.Layer))
-        self._c_layers = layers
+        self._c_layers = (layers, seconds)
         self._c_model, self._c_version = m, self.cache.version
         return m
 
