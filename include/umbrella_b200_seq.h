@@ -219,7 +219,7 @@ typedef struct umbs_layer_s {
     /* a second mixer beside the first: both read the same normed input, the layer adds
      * mix_scale * first + second_scale * second.  Only its mixer fields are read (no norms, no feed-forward). */
     const struct umbs_layer_s* second;
-    float mix_scale, second_scale;      /* 0 reads as 1 */
+    float mix_scale, second_scale;      /* read only with a second mixer */
 } umbs_layer_t;
 
 typedef struct {
@@ -392,7 +392,7 @@ typedef struct {
     const float* shared_gate;  /* fp32 [n] */
     const float* scale;        /* fp32 [width] */
     float mult;
-    float delta_mult;          /* factor on delta alone (0 reads as 1) */
+    float delta_mult;          /* factor on delta alone (with delta2 == NULL, 0 reads as 1) */
     const float* delta2;       /* fp32 [n, width] or NULL: a second dense part, added as delta2_mult * delta2 */
     float delta2_mult;
 } umbs_delta_t;
@@ -481,7 +481,7 @@ typedef struct {
     float* raw_out;            /* fp32 [n_tokens, heads M C, vdim] or NULL: the normalised outputs go here (no gate) instead of out */
 } umbs_attn_opts_t;
 
-/* umbs_cached_attention with umbs_attn_opts_t (NULL: none).  Pooled blocks go with none of the options. */
+/* umbs_cached_attention with the options above (opts NULL: none).  Pooled blocks go with none of the options. */
 int umbs_cached_attention_ex(int dtype, int mode, const void* q, const void* kv, const void* kv_cache, int kv_len,
                              const void* pool_cache, int pool_len, const umbs_batch_t* batch, int heads, int kv_heads, int dim,
                              int vdim, int window, int pool, float scale, const float* head_bias, const float* gate,

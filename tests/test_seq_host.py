@@ -238,3 +238,53 @@ def test_state_cache_of_windowless_latent_attention():
     assert float(c.ring[0][1, 23].min()) == 4.0 and float(c.ring[0][1, 24:].abs().max()) == 0
     s = [c.alloc_slot() for _ in range(3)]
     assert c.slots == 4 and c.ring[0].shape == (4, 48, 48) and float(c.ring[0][1, 23].min()) == 4.0
+
+
+# ---------------------------------------------------------------------------------------------- the Subivik family
+def test_subivik_config_reader_and_tensor_names():
+    import sub_helpers as SH
+    from umbrella_b200.models.subivik import layer_tensor_names, spec_from_config
+    spec = spec_from_config(SH.MIXED)
+    assert spec.norm_kind == "dyt" and spec.pos_embed == "sinusoid" and spec.width == 80 and spec.norm_eps == 1e-5
+    a, p, b = spec.layers[0], spec.layers[1], spec.layers[2]
+    assert (a.mixer, a.maps, a.chunk, a.kv_heads, a.diff, a.head_unit_norm, a.qk_norm, a.gate_kind) == \
+        ("cached_attention", 2, 16, 2, 0.25, True, True, 2)
+    assert (a.mlp.route, a.mlp.experts, a.mlp.top, a.mlp.route_scale, a.mlp.act) == ("softmax_all", 5, 2, 1.7, "silu")
+    assert (p.mixer, p.talk, p.dist_bias, p.softcap, p.maps, p.chunk) == ("cached_attention", True, True, 6.0, 1, 0)
+    assert (p.second.mixer, p.second.heads, p.second.dim, p.second.vdim) == ("time_mix", 3, 20, 20)
+    assert (p.mix_scale, p.second_scale, p.mlp.plain, p.mlp.shared_ff) == (0.6, 1.3, "xielu", 48)
+    assert b.kv_from == 0 and b.chunk == 24 and b.mlp is None and spec.layers[3].softcap == 0.0 and spec.layers[4].chunk == 0
+    n0, n1, n2 = (layer_tensor_names(spec, i) for i in range(3))
+    assert n0["q_norm"] == "l0.mix.q.norm" and n0["k"] == "l0.mix.k" and n0["experts"][4][2] == "l0.mlp.e4.down"
+    assert n1["talk"] == "l1.mix.left.talk" and n1["second"]["mu_w"] == "l1.mix.right.mu.w" and n1["dense_act"] == "l1.mlp.act"
+    assert "k" not in n2 and "k_norm" not in n2 and "norm2" not in n2 and n2["lq2"] == "l2.mix.lq2"
+    every = set()
+    for i in range(len(spec.layers)):
+        def walk(v):
+            if isinstance(v, dict):
+                [walk(x) for x in v.values()]
+            elif isinstance(v, (list, tuple)):
+                [walk(x) for x in v]
+            else:
+                every.add(v)
+        walk(layer_tensor_names(spec, i))
+    assert every | {"embed", "final.norm", "final.norm.b", "final.norm.alpha"} == set(SH.random_tensors(SH.MIXED))
+    bad = dict(SH.MIXED, layers=[SH.attention(2, 1, 8, 8, kv_from=0)])
+    with pytest.raises(ValueError):
+        spec_from_config(bad)                                       # a layer cannot borrow from itself or a later one
+
+
+def test_state_cache_of_subivik_layers():
+    import sub_helpers as SH
+    from umbrella_b200.attn.state_cache import SequenceStateCache
+    from umbrella_b200.models.subivik import spec_from_config
+    spec = spec_from_config(SH.MIXED)
+    c = SequenceStateCache(spec, slots=2, device="cpu", dtype=torch.float32, capacity=32)
+    assert len(c.units) == 8 and spec.layers[1].second.state_index == 6 and spec.layers[3].second.state_index == 7
+    assert c.kv_cache[0].shape == (2, 24, 2 * (2 * 12 + 20))        # a ring as long as the borrower's wider chunk
+    assert c.kv_cache[1].shape == (2, 32, 3 * (10 + 14))            # the whole sequence
+    assert c.kv_cache[2] is None and c.kv_cache[5] is None          # borrowers keep nothing
+    assert c.kv_cache[4].shape == (2, 32, 16 + 16 + 16)
+    assert c.tm_state[6].shape == (2, 3, 20, 20) and c.shift[6].shape == (2, 2, 80) and c.shift[1] is None
+    c.reserve_length(70)
+    assert c.capacity == 128 and c.kv_cache[0].shape[1] == 24 and c.kv_cache[1].shape[1] == 128 and c.kv_cache[4].shape[1] == 128

@@ -18,11 +18,11 @@ Every live sequence owns one slot.  A slot holds, per layer,
     fp32 [heads, dim (vdim + 1) + 1];
   * time-mix layers: per head the matrix memory, fp32 [heads, dim, dim] (key index first), and the previous token's
     normed activations in the token-shift state.
+and on the host its position (tokens fed so far) and parity.
 A cached-attention layer with several maps per head keeps [kv_heads (maps dim + vdim)] numbers per token; one with a
-chunked mask needs a ring of one chunk only; one that borrows another layer's keys and values keeps nothing.  A layer's
-second mixer (two mixers side by side) has state of its own, kept behind the layers' in the same lists
-(``spec.layers[i].second.state_index``).
-and on the host its position (tokens fed so far) and parity.  Nothing is cleared when a slot is freed or handed out
+chunked mask needs a ring of one chunk only; one that borrows another layer's keys and values keeps nothing (the lender's
+ring reaches as far back as its furthest-seeing borrower reads).  A layer's second mixer (two mixers side by side) has
+state of its own, kept behind the layers' in the same lists (``spec.layers[i].second.state_index``).  Nothing is cleared when a slot is freed or handed out
 again: the kernels read a sequence's state as zero while its position is 0, and a ring row is only ever read for a
 position that the current owner has written.
 """
@@ -48,8 +48,12 @@ class SequenceStateCache:
             if getattr(l, "second", None) is not None:
                 l.second.state_index = len(self.units)
                 self.units.append(l.second)
-        self._growing = any((l.mixer == "cached_attention" and l.kv_from is None and
-                             ((l.window <= 0 and l.chunk <= 0) or l.pool > 0)) or
+        # a layer that lends its keys and values keeps them as far back as its furthest-seeing borrower asks
+        self._borrowers = {}
+        for l in self.units:
+            if l.mixer == "cached_attention" and l.kv_from is not None:
+                self._borrowers.setdefault(id(spec.layers[l.kv_from]), []).append(l)
+        self._growing = any((l.mixer == "cached_attention" and l.kv_from is None and (self._reach(l) is None or l.pool > 0)) or
                             (l.mixer == "latent_attention" and l.window <= 0) for l in self.units)
         n = len(self.units)
         self.kv_cache: list[torch.Tensor | None] = [None] * n
@@ -76,8 +80,18 @@ class SequenceStateCache:
     def kv_len(self, layer) -> int:
         """Rows of a cached-attention layer's key/value cache per slot: the furthest key a row can see -- its window, or
         its chunk -- bounds the ring; without either, a row per token."""
-        reach = [int(n) for n in (layer.window, layer.chunk) if n > 0]
-        return max(min(reach), int(layer.pool), 1) if reach else self.capacity
+        reach = self._reach(layer)
+        return max(reach, int(layer.pool), 1) if reach is not None else self.capacity
+
+    def _reach(self, layer):
+        """How many positions back the rows of ``layer``'s cache are read, by itself and its borrowers; None: any."""
+        most = 0
+        for l in [layer] + self._borrowers.get(id(layer), []):
+            own = [int(n) for n in (l.window, l.chunk) if n > 0]
+            if not own:
+                return None
+            most = max(most, min(own))
+        return most
 
     def pool_len(self, layer) -> int:
         return max(1, -(-self.capacity // int(layer.pool))) if layer.pool > 0 else 0

@@ -340,8 +340,11 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
         }
         pend = umbs_delta_t{};
         pend.delta = s.mix_out; pend.scale = l.out_scale; pend.mult = mult;
-        pend.delta_mult = l.mix_scale != 0.f ? l.mix_scale : 1.f;
-        if (l.second != nullptr) { pend.delta2 = s.mix_out2; pend.delta2_mult = l.second_scale != 0.f ? l.second_scale : 1.f; }
+        pend.delta_mult = 1.f;
+        if (l.second != nullptr) {           // two mixers side by side: both factors as given (0 is a factor like any other)
+            pend.delta_mult = l.mix_scale;
+            pend.delta2 = s.mix_out2; pend.delta2_mult = l.second_scale;
+        }
         has_pend = true;
         if (l.has_mlp) {
             const umbs_mlp_t& f = l.mlp;

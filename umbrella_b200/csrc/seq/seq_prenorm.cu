@@ -375,7 +375,7 @@ extern "C" int umbs_add_norm_ex(int dtype, float* x, const umbs_delta_t* d, cons
     if (threads < 64) threads = 64;
     umbs_delta_t dd{};
     if (d != nullptr) dd = *d;
-    if (dd.delta_mult == 0.f) dd.delta_mult = 1.f;
+    if (dd.delta_mult == 0.f && dd.delta2 == nullptr) dd.delta_mult = 1.f;
     UMBS_DISPATCH_T(dtype, add_norm_kernel<T><<<n, threads, 0, st>>>(x, dd, d != nullptr, rows, kind, w, b, w_offset, alpha, width,
                                                                      eps, (T*)y, copy));
     count_launches(1);

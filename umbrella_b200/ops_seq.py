@@ -349,3 +349,115 @@ def embedding_scaled(ids, table, scale: float):
     S.check(S.load().umbs_embedding_scaled(_mode(table), _p(ids), _p(table), float(scale), _p(y), ids.numel(), table.shape[1],
                                            _stream()), "embedding_scaled")
     return y
+
+
+# ---------------------------------------------------------------------------------------------- score options, time mix
+def embedding_pos(ids, tok_pos, table, pos_freq, scale: float = 1.0):
+    """table[ids] * scale + sinusoidal positions (entry 2i: sin(p f_i), entry 2i + 1: cos(p f_i)); fp32 [n, width]."""
+    y = torch.empty((ids.numel(), table.shape[1]), dtype=torch.float32, device=table.device)
+    S.check(S.load().umbs_embedding_pos(_mode(table), _p(ids), _p(tok_pos), _p(table), float(scale), _p(pos_freq), _p(y),
+                                        ids.numel(), table.shape[1], _stream()), "embedding_pos")
+    return y
+
+
+def add_norm_dyt(x, w, b, alpha: float, dtype=torch.float32, rows=None, delta=None, delta_mult: float = 1.0, delta2=None,
+                 delta2_mult: float = 1.0):
+    """x [n, width] fp32 += delta_mult delta + delta2_mult delta2 (in place when ``rows`` is None), then
+    tanh(alpha x) w + b as ``dtype``."""
+    n = x.shape[0] if rows is None else rows.numel()
+    y = torch.empty((n, x.shape[1]), dtype=dtype, device=x.device)
+    d = None
+    if delta is not None or delta2 is not None:
+        d = S.Delta()
+        d.delta, d.delta2 = (t.data_ptr() if t is not None else None for t in (delta, delta2))
+        d.mult, d.delta_mult, d.delta2_mult = 1.0, float(delta_mult), float(delta2_mult)
+    S.check(S.load().umbs_add_norm_ex(_mode(y), _p(x), C.byref(d) if d is not None else None, _p(rows), n, S.UMBS_NORM_DYT,
+                                      _p(w), _p(b), 0.0, float(alpha), x.shape[1], 0.0, _p(y), None, _stream()), "add_norm_ex")
+    return y
+
+
+def attention_prep_maps(proj, batch: RaggedBatch, heads, kv_heads, dim, vdim, maps=1, q_norm=None, k_norm=None, eps=1e-6,
+                        dtype=torch.float32):
+    """proj fp32 [T, q (heads maps dim) | k (kv_heads maps dim) | v (kv_heads vdim) | ...] -> (q, kv) as ``dtype``, every
+    (head, map) of q and k RMS-normed with the weights given.  kv_heads 0: queries only (kv is None)."""
+    T = proj.shape[0]
+    q = torch.empty((T, heads * maps * dim), dtype=dtype, device=proj.device)
+    kv = torch.empty((T, kv_heads * (maps * dim + vdim)), dtype=dtype, device=proj.device) if kv_heads else None
+    S.check(S.load().umbs_attention_prep_ex(_mode(q), _p(proj), proj.stride(0), None, C.byref(batch.c), heads, kv_heads, dim, vdim,
+                                            0, 1, None, None, 0, 0, None, 1.0, maps, _p(q_norm), _p(k_norm), float(eps), _p(q),
+                                            _p(kv), _stream()), "attention_prep_ex")
+    return q, kv
+
+
+def scored_attention(q, kv, kv_cache, batch: RaggedBatch, heads, kv_heads, dim, vdim, scale, window=0, softcap=0.0, r1=None,
+                     r2=None, chunk=0, maps=1, talk=None, diff_lambda=0.0, unit_norm=False, eps=1e-6, out_mult=1.0, gate=None,
+                     append=True, split=True):
+    """Cached attention with score options, then umbs_attention_finish: a tanh cap, a distance penalty, a chunked mask,
+    two maps per head (a1 - diff_lambda a2) or softmax weights mixed across heads by ``talk``; unit RMS per head, a factor,
+    an element-wise sigmoid gate.  -> [T, heads vdim] as q's dtype."""
+    T = q.shape[0]
+    lib, row = S.load(), kv_heads * (maps * dim + vdim)
+    vheads = kv_heads if talk is not None else 1
+    raw = torch.empty((T, heads * maps * vheads, vdim), dtype=torch.float32, device=q.device)
+    out = torch.empty((T, heads * vdim), dtype=q.dtype, device=q.device)
+    o = S.AttnOpts()
+    o.softcap, o.dist_r1, o.dist_r2, o.chunk, o.maps, o.value_heads = float(softcap), r1.data_ptr() if r1 is not None else None, \
+        r2.data_ptr() if r2 is not None else None, chunk, maps, vheads
+    o.raw_out = raw.data_ptr()
+    part = torch.empty(2048 * (vdim + 2), dtype=torch.float32, device=q.device) if split else None
+    S.check(lib.umbs_cached_attention_ex(_mode(q), S.UMBS_ATTN_SOFTMAX, _p(q), _p(kv), _p(kv_cache), kv_cache.shape[1], None, 0,
+                                         C.byref(batch.c), heads, kv_heads, dim, vdim, window, 0, float(scale), None, None, 0, 0,
+                                         C.byref(o), _p(part), part.numel() * 4 if part is not None else 0, None, _stream()),
+            "cached_attention_ex")
+    S.check(lib.umbs_attention_finish(_mode(q), _p(raw), T, heads, kv_heads, vdim, maps, vheads, _p(talk), float(diff_lambda),
+                                      int(unit_norm), float(eps), float(out_mult), _p(gate), gate.stride(0) if gate is not None else 0,
+                                      _p(out), _stream()), "attention_finish")
+    if append:
+        S.check(lib.umbs_ring_append(_mode(q), _p(kv), _p(kv_cache), kv_cache.shape[1], C.byref(batch.c), row, _stream()),
+                "ring_append")
+    return out
+
+
+def shift_mix(h, mu, shift_state, batch: RaggedBatch):
+    """h [T, width] -> [T, n_mix, width]: h + (previous row - h) mu[s]; shift_state fp32 [2, slots, width]."""
+    out = torch.empty((h.shape[0], mu.shape[0], h.shape[1]), dtype=h.dtype, device=h.device)
+    S.check(S.load().umbs_shift_mix(_mode(h), _p(h), _p(mu), mu.shape[0], _p(shift_state), shift_state.shape[1], C.byref(batch.c),
+                                    h.shape[1], _p(out), _stream()), "shift_mix")
+    return out
+
+
+def time_mix(proj, decay_raw, decay_bias, bonus, batch: RaggedBatch, heads, dim, eps, out_norm_w, state, dtype=torch.float32):
+    """proj fp32 [T, r | k | v | g] and decay_raw fp32 [T, heads dim] -> [T, heads dim] as ``dtype``; state fp32
+    [slots, heads, dim, dim]."""
+    T = proj.shape[0]
+    o32 = torch.empty((T, heads * dim), dtype=torch.float32, device=proj.device)
+    out = torch.empty((T, heads * dim), dtype=dtype, device=proj.device)
+    S.check(S.load().umbs_time_mix(_mode(out), _p(proj), proj.stride(0), _p(decay_raw), _p(decay_bias), _p(bonus), C.byref(batch.c),
+                                   heads, dim, float(eps), _p(out_norm_w), _p(state), _p(o32), _p(out), _stream()), "time_mix")
+    return out
+
+
+def gemm_unary(a: torch.Tensor, w: torch.Tensor, unary: int, p0: float = 0.0, p1: float = 0.0, out_f32: bool = False):
+    """unary(a [M, K] x w [N, K]^T): UMBS_UNARY_TANH or UMBS_UNARY_XIELU with its two coefficients."""
+    assert w.dtype == a.dtype and a.stride(-1) == 1 and w.is_contiguous()
+    out = torch.empty((a.shape[0], w.shape[0]), dtype=torch.float32 if out_f32 else a.dtype, device=a.device)
+    S.check(S.load().umbs_gemm_unary(_mode(a), _p(a), a.stride(0), 0, _p(w), w.stride(0), 0, _p(out), out.stride(0), 0,
+                                     int(out_f32), a.shape[0], w.shape[0], w.shape[1], 1, None, unary, float(p0), float(p1),
+                                     _stream()), "gemm_unary")
+    return out
+
+
+def moe_route_scaled(h, w_router, top: int, mode: int, weight_scale: float = 1.0):
+    """``moe_route_ex`` with a factor on the chosen weights (UMBS_ROUTE_SOFTMAX_ALL: softmax over every expert)."""
+    n, width = h.shape
+    E = w_router.shape[0]
+    dev = h.device
+    sel_w = torch.empty((n, top), dtype=torch.float32, device=dev)
+    grp_off = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    pair_tok = torch.empty(n * top, dtype=torch.int32, device=dev)
+    pair_pos = torch.empty(n * top, dtype=torch.int32, device=dev)
+    scratch = torch.empty(2 * E + n * top, dtype=torch.int32, device=dev)
+    S.check(S.load().umbs_moe_route_scaled(_mode(h), _p(h), n, width, _p(w_router), E, top, mode, 1, 1, float(weight_scale),
+                                           _p(sel_w), _p(grp_off), _p(pair_tok), _p(pair_pos), _p(scratch), None, None,
+                                           _stream()), "moe_route_scaled")
+    return sel_w, grp_off, pair_tok, pair_pos, scratch[2 * E:].view(n, top)
