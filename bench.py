@@ -17,6 +17,7 @@ scripted acceptance with the reference's DEFAULT_ACC (random weights make draft 
   radanex            the sequence-state decoder family next to Llama at equal size (prefill / decode tokens/s, kernel table)
   zedotar            the pre-norm hybrid family (cached attention kinds, mLSTM) next to Radanex at equal size
   kulisun            the latent-attention family with a shared rotated key part and a group-limited router next to Radanex
+  subivik            the family of talking / differential attention beside a time-mix memory next to Zedotar at equal size
   static70b_b200tree the default workload on the packaged B200-tuned 16-node tree (sequoia_utils.generate_budget_tree)
 
 A *step* is one speculative-decoding iteration (draft build_tree + target verify + accept + KV gather).  ``value`` =
@@ -73,6 +74,7 @@ WORKLOADS["stochastic32k_hbm"] = dict(WORKLOADS["stochastic32k"], kv_host_layers
 WORKLOADS["radanex"] = dict(text="Radanex bf16 vs Llama fp16 at equal width / depth: prefill and decode tokens/s, kernel table")
 WORKLOADS["zedotar"] = dict(text="Zedotar bf16 vs Radanex bf16 at equal width / depth: prefill and decode tokens/s, kernel table")
 WORKLOADS["kulisun"] = dict(text="Kulisun bf16 vs Radanex bf16 at equal width / depth: prefill and decode tokens/s, kernel table")
+WORKLOADS["subivik"] = dict(text="Subivik bf16 vs Zedotar bf16 at equal width / depth: prefill and decode tokens/s, kernel table")
 E2E_REQUESTS = 8          # per replica (2 for stochastic32k: a 30k-token prefill and PCIe-bound verifies per request)
 
 
@@ -500,6 +502,9 @@ def main():
     if args.workload == "kulisun":
         from umbrella_b200 import seq_bench
         return seq_bench.run_kulisun(args)
+    if args.workload == "subivik":
+        from umbrella_b200 import seq_bench
+        return seq_bench.run_subivik(args)
     run_ours(args)
 
 

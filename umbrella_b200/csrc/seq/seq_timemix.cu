@@ -4,11 +4,11 @@
 //
 //   umbs_shift_mix : out[t, s, :] = h[t] + (h[t - 1] - h[t]) mu[s, :] for n_mix mixes; the row before a step's first
 //                    token comes from the slot's double-buffered shift state, the step's last row goes there.
-//   umbs_time_mix  : the recurrence, one warp per (sequence, head, 32 value columns): a lane owns a value column and keeps
-//                    that column of the state -- dim numbers -- in registers for the whole step; r, k and the decay of the
-//                    next 8 tokens are staged in shared memory (the decay's two exponentials are taken there, once per
-//                    token and channel).  Tokens run in order, so a prompt in one piece, in portions or token by token
-//                    performs the same additions.  A second kernel takes unit RMS per head, the weight and the silu gate.
+//   umbs_time_mix  : the recurrence, one block per (sequence, head, 32 value columns) whose warps each keep 16 key rows of
+//                    those columns in registers for the whole step; r, k and the decay of the next 16 tokens are staged in
+//                    shared memory (the decay's two exponentials are taken there, once per token and channel).  Tokens run
+//                    in order, so a prompt in one piece, in portions or token by token performs the same additions.  A
+//                    second kernel takes unit RMS per head, the weight and the silu gate.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
@@ -36,64 +36,107 @@ __global__ void shift_mix_kernel(const T* __restrict__ h, const float* __restric
     }
 }
 
-constexpr int kTmTok = 8;            // tokens staged at a time
+constexpr int kTmTok = 16;           // tokens staged at a time
+constexpr int kTmRows = 16;          // key rows of the state a warp keeps (per lane: one value column of them)
 
-// D: the head size rounded up to a multiple of 32 (registers per lane); dim: the real one
-template <int D>
-__global__ void __launch_bounds__(32) time_mix_kernel(const float* __restrict__ proj, int64_t ld, const float* __restrict__ decay_raw,
-                                                      const float* __restrict__ decay_bias, const float* __restrict__ bonus, Batch b,
-                                                      int heads, int dim, float* __restrict__ state, float* __restrict__ o) {
-    __shared__ __align__(16) float sr[kTmTok][D], sk[kTmTok][D], sw[kTmTok][D], su[D];
-    const int lane = threadIdx.x, j = blockIdx.x * 32 + lane, h = blockIdx.y, s = blockIdx.z;
+// One block = (32 value columns, head, sequence); warp w keeps key rows [16 w, 16 w + 16) of those columns in registers for
+// the whole step.  Per 16 tokens: r, k and the decay (its two exponentials taken here, once per token and channel) are
+// staged in shared memory; every warp walks the tokens in order over its rows -- read-out with the bonus first, then decay
+// and the token's own outer product -- and leaves its partial read-outs in shared memory, where they are added up warp
+// by warp.  The order of every addition is fixed by the layout alone, so a token's result does not depend on how the
+// sequence was cut into steps.
+__global__ void __launch_bounds__(256) time_mix_kernel(const float* __restrict__ proj, int64_t ld, const float* __restrict__ decay_raw,
+                                                       const float* __restrict__ decay_bias, const float* __restrict__ bonus, Batch b,
+                                                       int heads, int dim, float* __restrict__ state, float* __restrict__ o) {
+    extern __shared__ __align__(16) float tm_sm[];
+    const int nw = blockDim.x >> 5, Dp = nw * kTmRows;              // Dp >= dim: the staged rows, zero beyond dim
+    float* sr = tm_sm;                                              // [kTmTok][Dp]
+    float* sk = sr + kTmTok * Dp;
+    float* sw = sk + kTmTok * Dp;
+    float* su = sw + kTmTok * Dp;                                   // [Dp]
+    float* part = su + Dp;                                          // [kTmTok][nw][32]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int j = blockIdx.x * 32 + lane, h = blockIdx.y, s = blockIdx.z, k0 = warp * kTmRows;
     const int start = b.seq_start[s], len = b.seq_len[s], pos0 = b.seq_pos0[s], slot = b.seq_slot[s];
     const int hd = heads * dim;
     const bool col = j < dim;
-    float S[D];
+    float S[kTmRows];
     float* st = state + (((int64_t)slot * heads + h) * dim) * dim;          // S[k][j] at st[k dim + j]
 #pragma unroll
-    for (int k = 0; k < D; ++k) S[k] = (pos0 > 0 && col && k < dim) ? st[(int64_t)k * dim + j] : 0.f;
-    for (int k = lane; k < D; k += 32) su[k] = k < dim ? bonus[h * dim + k] : 0.f;
+    for (int i = 0; i < kTmRows; ++i) S[i] = (pos0 > 0 && col && k0 + i < dim) ? st[(int64_t)(k0 + i) * dim + j] : 0.f;
+    for (int k = tid; k < Dp; k += blockDim.x) su[k] = k < dim ? bonus[h * dim + k] : 0.f;
+    // what a thread stages per 16 tokens: kTmStage (token, row) pairs of r, k and the decay's argument, fetched one round
+    // of tokens ahead so that the loads fly while the current round is walked
+    constexpr int kTmStage = kTmTok * kTmRows / 32;
+    float pr[kTmStage], pk[kTmStage], pw[kTmStage], v[kTmTok], vn[kTmTok];
+    auto fetch = [&](int t0) {
+        const int nt = min(kTmTok, len - t0);
+#pragma unroll
+        for (int e = 0; e < kTmStage; ++e) {
+            const int i = tid + e * blockDim.x, tt = i / Dp, k = i - tt * Dp;
+            pr[e] = pk[e] = 0.f;
+            pw[e] = INFINITY;                                       // exp(-exp(inf)) = 0: rows beyond dim stay zero
+            if (tt < nt && k < dim) {
+                const int64_t t = start + t0 + tt;
+                pr[e] = proj[t * ld + h * dim + k];
+                pk[e] = proj[t * ld + hd + h * dim + k];
+                pw[e] = decay_raw[t * hd + h * dim + k] + decay_bias[h * dim + k];
+            }
+        }
+#pragma unroll
+        for (int tt = 0; tt < kTmTok; ++tt)
+            vn[tt] = (col && tt < nt) ? proj[(int64_t)(start + t0 + tt) * ld + 2 * hd + h * dim + j] : 0.f;
+    };
+    fetch(0);
     for (int t0 = 0; t0 < len; t0 += kTmTok) {
         const int nt = min(kTmTok, len - t0);
-        __syncwarp();
-        for (int i = lane; i < nt * D; i += 32) {
-            const int tt = i / D, k = i - tt * D;
-            const int64_t t = start + t0 + tt;
-            float r = 0.f, kk = 0.f, w = 0.f;
-            if (k < dim) {
-                r = proj[t * ld + h * dim + k];
-                kk = proj[t * ld + hd + h * dim + k];
-                w = expf(-expf(decay_raw[t * hd + h * dim + k] + decay_bias[h * dim + k]));
-            }
-            sr[tt][k] = r; sk[tt][k] = kk; sw[tt][k] = w;
-        }
-        __syncwarp();
-        for (int tt = 0; tt < nt; ++tt) {
-            const int64_t t = start + t0 + tt;
-            const float v = col ? proj[t * ld + 2 * hd + h * dim + j] : 0.f;
-            float acc = 0.f;
+        __syncthreads();                                            // the previous 16 tokens are consumed
 #pragma unroll
-            for (int k4 = 0; k4 < D; k4 += 4) {
-                const float4 r4 = *reinterpret_cast<const float4*>(&sr[tt][k4]);
-                const float4 k4v = *reinterpret_cast<const float4*>(&sk[tt][k4]);
-                const float4 w4 = *reinterpret_cast<const float4*>(&sw[tt][k4]);
-                const float4 u4 = *reinterpret_cast<const float4*>(&su[k4]);
-                const float ra[4] = {r4.x, r4.y, r4.z, r4.w}, ka[4] = {k4v.x, k4v.y, k4v.z, k4v.w};
+        for (int e = 0; e < kTmStage; ++e) {
+            const int i = tid + e * blockDim.x;
+            sr[i] = pr[e]; sk[i] = pk[e]; sw[i] = expf(-expf(pw[e]));
+        }
+#pragma unroll
+        for (int tt = 0; tt < kTmTok; ++tt) v[tt] = vn[tt];
+        __syncthreads();
+        if (t0 + kTmTok < len) fetch(t0 + kTmTok);
+#pragma unroll
+        for (int tt = 0; tt < kTmTok; ++tt) {
+            if (tt >= nt) break;
+            const float* rr = sr + tt * Dp + k0;
+            const float* kr = sk + tt * Dp + k0;
+            const float* wr = sw + tt * Dp + k0;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i4 = 0; i4 < kTmRows; i4 += 4) {
+                const float4 r4 = *reinterpret_cast<const float4*>(rr + i4);
+                const float4 k4 = *reinterpret_cast<const float4*>(kr + i4);
+                const float4 w4 = *reinterpret_cast<const float4*>(wr + i4);
+                const float4 u4 = *reinterpret_cast<const float4*>(su + k0 + i4);
+                const float ra[4] = {r4.x, r4.y, r4.z, r4.w}, ka[4] = {k4.x, k4.y, k4.z, k4.w};
                 const float wa[4] = {w4.x, w4.y, w4.z, w4.w}, ua[4] = {u4.x, u4.y, u4.z, u4.w};
 #pragma unroll
                 for (int x = 0; x < 4; ++x) {
-                    const float kv = ka[x] * v;
-                    acc = fmaf(ra[x], fmaf(ua[x], kv, S[k4 + x]), acc);
-                    S[k4 + x] = fmaf(wa[x], S[k4 + x], kv);
+                    const float kv = ka[x] * v[tt];
+                    acc[x] = fmaf(ra[x], fmaf(ua[x], kv, S[i4 + x]), acc[x]);
+                    S[i4 + x] = fmaf(wa[x], S[i4 + x], kv);
                 }
             }
-            if (col) o[t * hd + h * dim + j] = acc;
+            part[(tt * nw + warp) * 32 + lane] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        }
+        __syncthreads();
+        for (int i = tid; i < nt * 32; i += blockDim.x) {
+            const int tt = i >> 5, ln = i & 31, jj = blockIdx.x * 32 + ln;
+            if (jj >= dim) continue;
+            float sum = 0.f;
+            for (int w = 0; w < nw; ++w) sum += part[(tt * nw + w) * 32 + ln];
+            o[(int64_t)(start + t0 + tt) * hd + h * dim + jj] = sum;
         }
     }
     if (col) {
 #pragma unroll
-        for (int k = 0; k < D; ++k)
-            if (k < dim) st[(int64_t)k * dim + j] = S[k];
+        for (int i = 0; i < kTmRows; ++i)
+            if (k0 + i < dim) st[(int64_t)(k0 + i) * dim + j] = S[i];
     }
 }
 
@@ -148,10 +191,9 @@ extern "C" int umbs_time_mix(int dtype, const float* proj, int64_t ld, const flo
     if (dim > 128) return UMB_ERR_UNSUPPORTED;              // a lane keeps a column of the state in registers
     cudaStream_t st = (cudaStream_t)stream;
     const dim3 grid((dim + 31) / 32, heads, batch->n_seqs);
-    if (dim <= 32) time_mix_kernel<32><<<grid, 32, 0, st>>>(proj, ld, decay_raw, decay_bias, bonus, *batch, heads, dim, state, o_scratch);
-    else if (dim <= 64) time_mix_kernel<64><<<grid, 32, 0, st>>>(proj, ld, decay_raw, decay_bias, bonus, *batch, heads, dim, state, o_scratch);
-    else if (dim <= 96) time_mix_kernel<96><<<grid, 32, 0, st>>>(proj, ld, decay_raw, decay_bias, bonus, *batch, heads, dim, state, o_scratch);
-    else time_mix_kernel<128><<<grid, 32, 0, st>>>(proj, ld, decay_raw, decay_bias, bonus, *batch, heads, dim, state, o_scratch);
+    const int nw = (dim + kTmRows - 1) / kTmRows, Dp = nw * kTmRows;
+    const size_t smem = ((size_t)3 * kTmTok * Dp + Dp + (size_t)kTmTok * nw * 32) * sizeof(float);
+    time_mix_kernel<<<grid, 32 * nw, smem, st>>>(proj, ld, decay_raw, decay_bias, bonus, *batch, heads, dim, state, o_scratch);
     const int pairs = batch->n_tokens * heads;
     if (dtype == UMBS_BF16)
         time_mix_finish_kernel<__nv_bfloat16><<<(pairs + 3) / 4, 128, 0, st>>>(o_scratch, proj, ld, pairs, heads, dim, eps, out_norm_w,

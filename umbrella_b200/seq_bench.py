@@ -634,3 +634,182 @@ def run_kulisun(args):
                        "l2": "whole-model runs stream more than L2 per step; kernel table flushes L2 between runs"},
             "sizes": sizes, "kernels": table}
     print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------- the Subivik family
+def subivik_config(width: int, layers: int = 8) -> dict:
+    """A Subivik config with the layer sizes of a model of this width: heads of 128 with a quarter as many key/value heads
+    for the talking attention, recurrent heads of 64 over the whole width beside it; differential attention with two maps
+    of 64 per head inside chunks of 1024, one of those layers borrowing an earlier one's keys and values; dense
+    feed-forward of 3 x width (the two matrices weigh what Zedotar's three of 2 x width do) or 2 of 16 experts."""
+    heads = max(2, width // 128)
+    kv = max(1, heads // 4)
+    par = dict(type="parallel", mixer=dict(left=dict(heads=heads, kv_heads=kv, dim=128, vdim=128, scale=128 ** -0.5, softcap=30.0),
+                                           right=dict(heads=width // 64, dim=64), left_scale=0.8, right_scale=0.9))
+    att = dict(type="attention", mixer=dict(heads=heads, kv_heads=kv, dim=64, vdim=128, scale=0.125, diff=0.3, mask=dict(size=1024)))
+    dense = dict(kind="dense", ff=3 * width)
+    moe = dict(kind="moe", router=dict(experts=16, top=2, scale=2.5), expert=dict(ff=width // 2))
+    plan, first_att = [], None
+    for i in range(layers):
+        if i % 4 == 1:
+            first_att = i if first_att is None else first_att
+            plan.append(dict(att, mlp=moe))
+        elif i % 4 == 3 and first_att is not None:
+            plan.append(dict(type="attention", mixer=dict(att["mixer"], kv_from=first_att), mlp=dense))
+        else:
+            plan.append(dict(par, mlp=moe if i % 4 == 2 else dense))
+    return dict(architecture="Subivik", width=width, vocab=32768, norm=dict(eps=1e-6), layers=plan)
+
+
+def bench_subivik(width, layers, device, prompt, ctx, batches, timer):
+    from .models.subivik import Subivik, spec_from_config
+    spec = spec_from_config(subivik_config(width, layers))
+    m = Subivik(spec, device=device, dtype=torch.bfloat16, slots=max(batches), max_tokens=prompt + ctx)
+    return bench_seq_model(m, spec, prompt, ctx, batches, timer)
+
+
+def kernel_table_subivik(sm, zm, device, timer, T=4096):
+    """Device time of each Subivik mechanism at prefill size (one sequence of T tokens) and at decode size (8 sequences
+    behind 512 tokens), with its roofline fractions, and the like kernel of the Zedotar path measured the same way in the
+    same run (``like`` names the pairing)."""
+    from . import _lib_seq as S, ops_seq as Q
+    hbm, tflops, how = _peaks()
+    sp, W = sm.spec, sm.spec.width
+    fp32_peak = 148 * 128 * 2 * 1.965e-3
+    rows = []
+
+    def add(name, ms, nbytes=0, flops=0, like=None, flops32=0):
+        r = dict(kernel=name, ms=round(ms, 4))
+        if flops32:
+            r["fp32_tflops"], r["frac_of_fp32_fma_peak"] = round(flops32 / ms / 1e9, 2), round(flops32 / ms / 1e9 / fp32_peak, 3)
+        if flops:
+            r["tflops"], r["frac_of_bf16_peak"] = round(flops / ms / 1e9, 1), round(flops / ms / 1e9 / tflops, 3)
+        if nbytes:
+            r["gb_s"], r["frac_of_hbm_peak"] = round(nbytes / ms / 1e6, 1), round(nbytes / ms / 1e6 / hbm, 3)
+        if like:
+            r["like"] = like
+        rows.append(r)
+    par = next(l for l in sp.layers if l.second is not None)
+    dif = next(l for l in sp.layers if l.maps == 2 and l.kv_from is None)
+    pw, dw = sm.weights[sp.layers.index(par)], sm.weights[sp.layers.index(dif)]
+    tm, tw = par.second, pw["second"]
+    dn = next(sm.weights[i] for i, l in enumerate(sp.layers) if l.mlp is not None and l.mlp.plain)
+    zsp = zm.spec
+    mls = next(l for l in zsp.layers if l.mixer == "mlstm")
+    zat = next(l for l in zsp.layers if l.mixer == "cached_attention" and l.window > 0)
+    mw, aw = (zm.weights[zsp.layers.index(l)] for l in (mls, zat))
+    bf = dict(dtype=torch.bfloat16, device=device)
+    ctx = 512
+    sm.cache.reserve_length(T)
+    zm.cache.reserve_length(T)
+    for n, tag in ((T, f"prefill T={T}"), (8, "decode T=8")):
+        nseq = 1 if n == T else 8
+        per = n // nseq
+        pos0 = 0 if n == T else ctx
+        batch = Q.RaggedBatch([(s, per, pos0, 0) for s in range(nseq)], device)
+        x, d, d2 = (torch.randn(n, W, device=device) for _ in range(3))
+        h = torch.randn(n, W, **bf)
+        # feed-forward product with its activation
+        up = dn["s_gu"]
+        p0, p1 = dn["unary_p"]
+        ms = timer(lambda: Q.gemm_unary(h, up, S.UMBS_UNARY_XIELU, p0, p1))
+        add(f"gemm dense up + xielu [{n} x {W}] x [{up.shape[0]} x {W}] ({tag})", ms,
+            nbytes=up.numel() * 2 + n * W * 2 + n * up.shape[0] * 2, flops=2 * n * W * up.shape[0], like="gemm dense gate|up + gelu")
+        gu = mw["s_gu"]
+        ms = timer(lambda: Q.gemm(h, gu, dual=S.UMBS_ACT_GELU_TANH))
+        add(f"zedotar gemm dense gate|up + gelu [{n} x {W}] x [{gu.shape[0]} x {W}] ({tag})", ms,
+            nbytes=gu.numel() * 2 + n * W * 2 + n * gu.shape[0], flops=2 * n * W * gu.shape[0])
+        # residual + norm
+        ms = timer(lambda: Q.add_norm_dyt(x, pw["norm"], pw["norm_b"], 0.7, torch.bfloat16, delta=d, delta_mult=0.8, delta2=d2, delta2_mult=0.9))
+        add(f"residual add of two mixers + tanh norm ({tag})", ms, nbytes=n * W * (4 + 4 + 4 + 4 + 2), like="residual add + rms norm")
+        ms = timer(lambda: Q.add_rms_norm(x, d, mw["norm"], 1.0, zsp.norm_eps, torch.bfloat16))
+        add(f"zedotar residual add + rms norm ({tag})", ms, nbytes=n * W * (4 + 4 + 4 + 2))
+        # token-shifted mixes
+        sstate = sm.cache.shift[tm.state_index]
+        ms = timer(lambda: Q.shift_mix(h, tw["mu"], sstate, batch))
+        add(f"five token-shifted mixes ({tag})", ms, nbytes=n * W * 2 * 6)
+        # the time-mix memory beside mLSTM
+        hd = tm.heads * tm.dim
+        proj, raw = torch.randn(n, 4 * hd, device=device), torch.randn(n, hd, device=device) - 1.0
+        tstate = sm.cache.tm_state[tm.state_index]
+        ms = timer(lambda: Q.time_mix(proj, raw, tw["w0"], tw["u"], batch, tm.heads, tm.dim, sp.norm_eps, tw["out_norm"], tstate, torch.bfloat16))
+        add(f"time mix: decay exponentials + recurrence + unit norm + gate, fp32, {tm.heads} heads of {tm.dim} ({tag})", ms,
+            nbytes=n * 5 * hd * 4 + n * hd * (4 + 4 + 2) + nseq * tm.heads * tm.dim * tm.dim * 8,
+            flops32=6 * n * tm.heads * tm.dim * tm.dim, like="mlstm")
+        ld = 2 * mls.heads * (mls.dim + mls.vdim) + 2 * mls.heads
+        mproj = torch.randn(n, ld, device=device)
+        mstate = zm.cache.mlstm_state[zsp.layers.index(mls)]
+        ms = timer(lambda: Q.mlstm(mproj, mw["bias_in"], batch, mls.heads, mls.dim, mls.vdim, mls.gate_cap, zsp.norm_eps, mw["out_norm"],
+                                   mstate, torch.bfloat16))
+        add(f"zedotar mlstm: gates + recurrence + normaliser + unit norm + gate, fp32, {mls.heads} heads of {mls.dim} x {mls.vdim} ({tag})", ms,
+            nbytes=n * ld * 4 + n * mls.heads * mls.vdim * (4 + 4 + 2) + nseq * mls.heads * mls.dim * (mls.vdim + 1) * 8,
+            flops32=4 * n * mls.heads * mls.dim * (mls.vdim + 1))
+        # the attention kinds
+        for l, w, name in ((par, pw, "causal, cap + distance penalty, talking heads"), (dif, dw, f"differential, chunks of {dif.chunk}")):
+            H, G, D, V, M = l.heads, l.kv_heads, l.dim, l.vdim, l.maps
+            C_ = G if l.talk else 1
+            cq, ck, cv, cg = H * M * D, G * M * D, G * V, (H * V if l.gate_kind else 0)
+            pr = torch.randn(n, cq + ck + cv + cg, device=device)
+            cache = sm.cache.kv_cache[l.state_index]
+            qn, kn = w.get("q_norm"), w.get("k_norm")
+            ms = timer(lambda: Q.attention_prep_maps(pr, batch, H, G, D, V, maps=M, q_norm=qn, k_norm=kn, eps=sp.norm_eps, dtype=torch.bfloat16))
+            add(f"attention prep{': norm of query and key maps' if qn is not None else ''} -> q, key|value rows ({name}; {tag})", ms,
+                nbytes=n * (cq + ck + cv) * 4 + n * (cq + ck + cv) * 2)
+            q, kv = Q.attention_prep_maps(pr, batch, H, G, D, V, maps=M, q_norm=qn, k_norm=kn, eps=sp.norm_eps, dtype=torch.bfloat16)
+            gate = pr[:, cq + ck + cv:] if cg else None
+            ms = timer(lambda: Q.scored_attention(q, kv, cache, batch, H, G, D, V, l.scale, softcap=l.softcap, r1=w.get("r1"), r2=w.get("r2"),
+                                                  chunk=l.chunk, maps=M, talk=w.get("talk"), diff_lambda=w.get("diff_lambda", 0.0),
+                                                  unit_norm=l.head_unit_norm, eps=sp.norm_eps, out_mult=0.7, gate=gate, append=False))
+            reach = l.chunk if l.chunk > 0 else 1 << 30
+            seen = lambda p: min(p + 1, p % reach + 1)
+            keys = sum(seen(p) for p in range(pos0, pos0 + per)) * nseq
+            kv_bytes = n * (ck + cv) * 2 if n == T else nseq * seen(pos0) * (ck + cv) * 2
+            add(f"cached attention + finish, {name}, fp32 scores, {H * M * C_} softmax rows per token ({tag})", ms,
+                nbytes=n * cq * 2 + kv_bytes + n * H * M * C_ * V * 8 + n * H * V * 2,
+                flops32=2 * keys * H * M * C_ * (D + V), like="zedotar cached attention")
+        H, G, D, V = zat.heads, zat.kv_heads, zat.dim, zat.vdim
+        zpr = torch.randn(n, H * D + G * (D + V) + H, device=device)
+        zi = zsp.layers.index(zat)
+        zcache, zpool = zm.cache.kv_cache[zi], zm.cache.pool_cache[zi]
+        q, kv = Q.attention_prep(zpr, aw.get("bias_in"), batch, H, G, D, V, zat.rot_dims, aw["inv_freq"], zat.rot_mag, False, 1, None, None,
+                                 torch.bfloat16)
+        zgate = zpr[:, H * D + G * (D + V):]
+        ms = timer(lambda: Q.cached_attention(q, kv, zcache, batch, H, G, D, V, zat.scale, mode=S.UMBS_ATTN_SOFTMAX_SINK, window=zat.window,
+                                              pool=zat.pool, pool_cache=zpool, gate=zgate, gate_per_head=True, append=False))
+        seen = lambda p: min(p + 1, zat.window) + (max(0, p - zat.window + 1) // zat.pool if zat.pool else 0)
+        keys = sum(seen(p) for p in range(pos0, pos0 + per)) * nseq
+        kv_bytes = n * G * (D + V) * 2 if n == T else nseq * seen(pos0) * G * (D + V) * 2
+        add(f"zedotar cached attention, window {zat.window} + blocks of {zat.pool}, sink, fp32 scores, {H} softmax rows per token ({tag})", ms,
+            nbytes=n * H * (D + V) * 2 + kv_bytes, flops32=2 * keys * H * (D + V))
+    return rows, how
+
+
+def run_subivik(args):
+    from . import _lib_seq
+    device = "cuda:0"
+    timer = Timer(device)
+    hbm, tflops, how = _peaks()
+    sizes, table = [], None
+    launches0 = _lib_seq.load().umbs_launch_count()
+    for width in (1024, 2048):
+        layers, prompt, ctx = 8, 2048, 512
+        sm, s = bench_subivik(width, layers, device, prompt, ctx, (1, 8, 64), timer)
+        zm, z = bench_zedotar(width, layers, device, prompt, ctx, (1, 8, 64), timer)
+        sizes.append({"width": width, "layers": layers, "subivik_bf16": {k: round(v, 3) for k, v in s.items()},
+                      "zedotar_bf16": {k: round(v, 3) for k, v in z.items()}})
+        if width == 2048:
+            table, _ = kernel_table_subivik(sm, zm, device, timer)
+        del sm, zm
+        torch.cuda.empty_cache()
+    launches = _lib_seq.load().umbs_launch_count() - launches0
+    head = sizes[-1]["subivik_bf16"]
+    line = {"metric": "decode tokens/sec at batch 64 (Subivik bf16, width 2048, 8 layers, synthetic weights)",
+            "value": head["decode_b64_tok_s"], "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic", "vs_baseline": None, "gpu_launches": int(launches),
+            "config": {"name": "subivik", "workload": "prefill 1 x 2048 and 4 x 2048 tokens; decode at batch 1 / 8 / 64 behind a "
+                       "512-token context; Zedotar bf16 (the closest family: pre-norm, cached attention, a recurrent matrix memory) "
+                       "of the same width and depth beside it",
+                       "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": how},
+                       "l2": "whole-model runs stream more than L2 per step; kernel table flushes L2 between runs"},
+            "sizes": sizes, "kernels": table}
+    print(json.dumps(line))
