@@ -21,10 +21,10 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from umbrella_b200.speculation.auto_engine import AutoEngine  # noqa: E402
 
 ap = argparse.ArgumentParser()
-ap.add_argument("--config", default=None, help="an engine config such as configs/b200_batch_radanex.json, configs/b200_batch_zedotar.json or configs/b200_batch_kulisun.json")
+ap.add_argument("--config", default=None, help="an engine config such as configs/b200_batch_radanex.json, configs/b200_batch_zedotar.json, configs/b200_batch_kulisun.json or configs/b200_batch_subivik.json")
 ap.add_argument("--model", default=None)
 ap.add_argument("--synthetic-width", type=int, default=0, help="build a synthetic config of this width instead")
-ap.add_argument("--family", default="radanex", choices=["radanex", "zedotar", "kulisun"], help="family of the synthetic config")
+ap.add_argument("--family", default="radanex", choices=["radanex", "zedotar", "kulisun", "subivik"], help="family of the synthetic config")
 ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
 ap.add_argument("--prompts", type=int, default=8)
 ap.add_argument("--prompt-len", type=int, default=128)
@@ -40,7 +40,7 @@ if args.model:
 if args.synthetic_width:
     from umbrella_b200 import seq_bench
     d = tempfile.mkdtemp(prefix=args.family + "_synth_")
-    make = {"zedotar": seq_bench.zedotar_config, "kulisun": seq_bench.kulisun_config}.get(args.family, seq_bench.radanex_config)
+    make = {"zedotar": seq_bench.zedotar_config, "kulisun": seq_bench.kulisun_config, "subivik": seq_bench.subivik_config}.get(args.family, seq_bench.radanex_config)
     json.dump(make(args.synthetic_width), open(os.path.join(d, "config.json"), "w"))
     config.update(model=d, synthetic=True)
 engine = AutoEngine.from_config("cuda:0", **config)

@@ -1,7 +1,7 @@
-"""One prefill step and a few eager decode steps of a synthetic Radanex (or Zedotar, or Kulisun) model: the program to put under
+"""One prefill step and a few eager decode steps of a synthetic Radanex (or Zedotar, Kulisun or Subivik) model: the program to put under
 `ncu --metrics gpu__time_duration.sum` for a launch list of the sequence-state step (small: < 1 GB on the device).
 
-    python scripts/seq_step_once.py [width] [batch] [context] [decode steps] [radanex|zedotar|kulisun]
+    python scripts/seq_step_once.py [width] [batch] [context] [decode steps] [radanex|zedotar|kulisun|subivik]
 """
 import os
 import sys
@@ -18,6 +18,9 @@ if len(sys.argv) > 5 and sys.argv[5] == "zedotar":
 elif len(sys.argv) > 5 and sys.argv[5] == "kulisun":
     from umbrella_b200.models.kulisun import Kulisun as Family, spec_from_config  # noqa: E402
     spec = spec_from_config(seq_bench.kulisun_config(width, 8))
+elif len(sys.argv) > 5 and sys.argv[5] == "subivik":
+    from umbrella_b200.models.subivik import Subivik as Family, spec_from_config  # noqa: E402
+    spec = spec_from_config(seq_bench.subivik_config(width, 8))
 else:
     from umbrella_b200.models.radanex import Radanex as Family, spec_from_config  # noqa: E402
     spec = spec_from_config(seq_bench.radanex_config(width, 8))
