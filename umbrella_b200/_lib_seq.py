@@ -1,7 +1,7 @@
 """ctypes binding of libumbrella_b200_seq.so (the C ABI declared in include/umbrella_b200_seq.h): the batched step
 of the sequence-state decoders and its building blocks.
 
-The library is compiled in-tree on first use when it is missing or older than its sources (``build.build_seq``: seven
+The library is compiled in-tree on first use when it is missing or older than its sources (``build.build_seq``: eight
 small translation units, seconds) -- a fresh checkout serves these models without a separate build step.  There is
 no PyTorch / CPU fallback behind these calls: without nvcc and without the library, loading is an error.
 """
