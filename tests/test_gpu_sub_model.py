@@ -229,3 +229,16 @@ def test_random_configurations(seed):
             got[i].append(o[i:i + 1])
     for i in range(3):
         assert H.row_err(torch.cat(got[i]), refs[i]) < TOL_DEEP, (seed, i)
+
+
+def test_bf16_at_sizes_no_tensor_core_tile_takes(mixed):
+    """bf16 with widths and head sizes that are no multiple of a tile: the products fall back to their plain kernels, the
+    cache rows are bf16, and a prompt cut into portions and decoded gives the numbers of the whole prompt within rounding."""
+    cfg, om, _ = mixed
+    pb = H.product_model(cfg, H.random_tensors(cfg, seed=1), torch.bfloat16)
+    seq = toks(120, cfg["vocab"], 41)
+    ref = O.forward(om, seq)[0]
+    whole, parts = run(pb, [seq]), run(pb, cut(seq, [50, 2, 31]) [:3] + [[x] for x in seq[83:]])
+    for a, b in ((whole, ref), (parts, ref), (parts, whole)):
+        rows = H.row_errs(a, b)
+        assert float(rows.median()) < 0.04 and float((rows > 0.15).double().mean()) < 0.05

@@ -5,8 +5,9 @@
 //   umbs_shift_mix : out[t, s, :] = h[t] + (h[t - 1] - h[t]) mu[s, :] for n_mix mixes; the row before a step's first
 //                    token comes from the slot's double-buffered shift state, the step's last row goes there.
 //   umbs_time_mix  : the recurrence, one block per (sequence, head, 32 value columns) whose warps each keep 16 key rows of
-//                    those columns in registers for the whole step; r, k and the decay of the next 16 tokens are staged in
-//                    shared memory (the decay's two exponentials are taken there, once per token and channel).  Tokens run
+//                    those columns in registers for the whole step; r, k, v and the decay of 16 tokens at a time are staged in
+//                    a ring of shared-memory stages by asynchronous copies (the decay's two exponentials are taken there, once
+//                    per token and channel).  Tokens run
 //                    in order, so a prompt in one piece, in portions or token by token performs the same additions.  A
 //                    second kernel takes unit RMS per head, the weight and the silu gate.
 #include <cuda_bf16.h>
@@ -36,76 +37,97 @@ __global__ void shift_mix_kernel(const T* __restrict__ h, const float* __restric
     }
 }
 
-constexpr int kTmTok = 16;           // tokens staged at a time
+constexpr int kTmTok = 16;           // tokens per group staged in shared memory
 constexpr int kTmRows = 16;          // key rows of the state a warp keeps (per lane: one value column of them)
+constexpr int kTmStages = 4;         // groups in flight: asynchronous copies run three groups ahead of the walk
+
+__device__ __forceinline__ void cp_async_f32(float* smem_dst, const float* gmem_src) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(gmem_src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
 // One block = (32 value columns, head, sequence); warp w keeps key rows [16 w, 16 w + 16) of those columns in registers for
-// the whole step.  Per 16 tokens: r, k and the decay (its two exponentials taken here, once per token and channel) are
-// staged in shared memory; every warp walks the tokens in order over its rows -- read-out with the bonus first, then decay
-// and the token's own outer product -- and leaves its partial read-outs in shared memory, where they are added up warp
-// by warp.  The order of every addition is fixed by the layout alone, so a token's result does not depend on how the
-// sequence was cut into steps.
+// the whole step.  Tokens are staged 16 at a time in a ring of four shared-memory stages filled by asynchronous copies
+// (r, k, the decay's argument and the block's 32 value columns), so that global latency is hidden although a scheduler
+// holds a single warp; the decay's two exponentials are taken in place when a stage has landed, once per token and
+// channel.  Every warp walks the tokens in order over its rows -- read-out with the bonus first, then decay and the token's
+// own outer product -- and leaves its partial read-outs in shared memory, where they are added up warp by warp.  The
+// order of every addition is fixed by the layout alone, so a token's result does not depend on how the sequence was cut
+// into steps.
 __global__ void __launch_bounds__(256) time_mix_kernel(const float* __restrict__ proj, int64_t ld, const float* __restrict__ decay_raw,
                                                        const float* __restrict__ decay_bias, const float* __restrict__ bonus, Batch b,
                                                        int heads, int dim, float* __restrict__ state, float* __restrict__ o) {
     extern __shared__ __align__(16) float tm_sm[];
     const int nw = blockDim.x >> 5, Dp = nw * kTmRows;              // Dp >= dim: the staged rows, zero beyond dim
-    float* sr = tm_sm;                                              // [kTmTok][Dp]
-    float* sk = sr + kTmTok * Dp;
-    float* sw = sk + kTmTok * Dp;
-    float* su = sw + kTmTok * Dp;                                   // [Dp]
+    const int plane = kTmTok * Dp, stage_floats = 3 * plane + kTmTok * 32;
+    float* su = tm_sm + kTmStages * stage_floats;                   // [Dp]
     float* part = su + Dp;                                          // [kTmTok][nw][32]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int j = blockIdx.x * 32 + lane, h = blockIdx.y, s = blockIdx.z, k0 = warp * kTmRows;
     const int start = b.seq_start[s], len = b.seq_len[s], pos0 = b.seq_pos0[s], slot = b.seq_slot[s];
     const int hd = heads * dim;
     const bool col = j < dim;
+    constexpr int kPerThread = kTmTok * kTmRows / 32;               // (token, row) pairs a thread stages per group
     float S[kTmRows];
     float* st = state + (((int64_t)slot * heads + h) * dim) * dim;          // S[k][j] at st[k dim + j]
 #pragma unroll
     for (int i = 0; i < kTmRows; ++i) S[i] = (pos0 > 0 && col && k0 + i < dim) ? st[(int64_t)(k0 + i) * dim + j] : 0.f;
     for (int k = tid; k < Dp; k += blockDim.x) su[k] = k < dim ? bonus[h * dim + k] : 0.f;
-    // what a thread stages per 16 tokens: kTmStage (token, row) pairs of r, k and the decay's argument, fetched one round
-    // of tokens ahead so that the loads fly while the current round is walked
-    constexpr int kTmStage = kTmTok * kTmRows / 32;
-    float pr[kTmStage], pk[kTmStage], pw[kTmStage], v[kTmTok], vn[kTmTok];
-    auto fetch = [&](int t0) {
-        const int nt = min(kTmTok, len - t0);
+    const int groups = (len + kTmTok - 1) / kTmTok;
+    // start the copies of group g into its stage (places without a token or beyond dim are zeroed by plain stores)
+    auto issue = [&](int g) {
+        float* sr = tm_sm + (g % kTmStages) * stage_floats;
+        float* sk = sr + plane;
+        float* sw = sk + plane;
+        float* sv = sw + plane;
+        const int t0 = g * kTmTok, nt = min(kTmTok, len - t0);
 #pragma unroll
-        for (int e = 0; e < kTmStage; ++e) {
+        for (int e = 0; e < kPerThread; ++e) {
             const int i = tid + e * blockDim.x, tt = i / Dp, k = i - tt * Dp;
-            pr[e] = pk[e] = 0.f;
-            pw[e] = INFINITY;                                       // exp(-exp(inf)) = 0: rows beyond dim stay zero
             if (tt < nt && k < dim) {
                 const int64_t t = start + t0 + tt;
-                pr[e] = proj[t * ld + h * dim + k];
-                pk[e] = proj[t * ld + hd + h * dim + k];
-                pw[e] = decay_raw[t * hd + h * dim + k] + decay_bias[h * dim + k];
+                cp_async_f32(sr + i, proj + t * ld + h * dim + k);
+                cp_async_f32(sk + i, proj + t * ld + hd + h * dim + k);
+                cp_async_f32(sw + i, decay_raw + t * hd + h * dim + k);
+            } else {
+                sr[i] = 0.f; sk[i] = 0.f; sw[i] = 0.f;
             }
         }
-#pragma unroll
-        for (int tt = 0; tt < kTmTok; ++tt)
-            vn[tt] = (col && tt < nt) ? proj[(int64_t)(start + t0 + tt) * ld + 2 * hd + h * dim + j] : 0.f;
-    };
-    fetch(0);
-    for (int t0 = 0; t0 < len; t0 += kTmTok) {
-        const int nt = min(kTmTok, len - t0);
-        __syncthreads();                                            // the previous 16 tokens are consumed
-#pragma unroll
-        for (int e = 0; e < kTmStage; ++e) {
-            const int i = tid + e * blockDim.x;
-            sr[i] = pr[e]; sk[i] = pk[e]; sw[i] = expf(-expf(pw[e]));
+        for (int i = tid; i < kTmTok * 32; i += blockDim.x) {
+            const int tt = i >> 5, jj = blockIdx.x * 32 + (i & 31);
+            if (tt < nt && jj < dim) cp_async_f32(sv + i, proj + (int64_t)(start + t0 + tt) * ld + 2 * hd + h * dim + jj);
+            else sv[i] = 0.f;
         }
+    };
+    for (int g = 0; g < kTmStages - 1; ++g) {
+        if (g < groups) issue(g);
+        cp_async_commit();
+    }
+    for (int g = 0; g < groups; ++g) {
+        // (the stage this writes was walked in the previous iteration, which ended with a barrier)
+        if (g + kTmStages - 1 < groups) issue(g + kTmStages - 1);
+        cp_async_commit();
+        cp_async_wait<kTmStages - 1>();                             // this thread's copies of group g have landed
+        float* sr = tm_sm + (g % kTmStages) * stage_floats;
+        float* sk = sr + plane;
+        float* sw = sk + plane;
+        float* sv = sw + plane;
+        const int t0 = g * kTmTok, nt = min(kTmTok, len - t0);
 #pragma unroll
-        for (int tt = 0; tt < kTmTok; ++tt) v[tt] = vn[tt];
+        for (int e = 0; e < kPerThread; ++e) {                      // the decay of the places this thread copied
+            const int i = tid + e * blockDim.x, tt = i / Dp, k = i - tt * Dp;
+            if (tt < nt && k < dim) sw[i] = expf(-expf(sw[i] + decay_bias[h * dim + k]));
+        }
         __syncthreads();
-        if (t0 + kTmTok < len) fetch(t0 + kTmTok);
 #pragma unroll
         for (int tt = 0; tt < kTmTok; ++tt) {
             if (tt >= nt) break;
             const float* rr = sr + tt * Dp + k0;
             const float* kr = sk + tt * Dp + k0;
             const float* wr = sw + tt * Dp + k0;
+            const float v = sv[tt * 32 + lane];
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i4 = 0; i4 < kTmRows; i4 += 4) {
@@ -117,7 +139,7 @@ __global__ void __launch_bounds__(256) time_mix_kernel(const float* __restrict__
                 const float wa[4] = {w4.x, w4.y, w4.z, w4.w}, ua[4] = {u4.x, u4.y, u4.z, u4.w};
 #pragma unroll
                 for (int x = 0; x < 4; ++x) {
-                    const float kv = ka[x] * v[tt];
+                    const float kv = ka[x] * v;
                     acc[x] = fmaf(ra[x], fmaf(ua[x], kv, S[i4 + x]), acc[x]);
                     S[i4 + x] = fmaf(wa[x], S[i4 + x], kv);
                 }
@@ -192,7 +214,13 @@ extern "C" int umbs_time_mix(int dtype, const float* proj, int64_t ld, const flo
     cudaStream_t st = (cudaStream_t)stream;
     const dim3 grid((dim + 31) / 32, heads, batch->n_seqs);
     const int nw = (dim + kTmRows - 1) / kTmRows, Dp = nw * kTmRows;
-    const size_t smem = ((size_t)3 * kTmTok * Dp + Dp + (size_t)kTmTok * nw * 32) * sizeof(float);
+    const size_t smem = ((size_t)kTmStages * (3 * kTmTok * Dp + kTmTok * 32) + Dp + (size_t)kTmTok * nw * 32) * sizeof(float);
+    static bool big_smem = false;                           // up to 123 KB for heads of 128: above the default limit
+    if (!big_smem) {
+        cudaError_t e = cudaFuncSetAttribute(time_mix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        big_smem = true;
+    }
     time_mix_kernel<<<grid, 32 * nw, smem, st>>>(proj, ld, decay_raw, decay_bias, bonus, *batch, heads, dim, state, o_scratch);
     const int pairs = batch->n_tokens * heads;
     if (dtype == UMBS_BF16)

@@ -644,11 +644,11 @@ def subivik_config(width: int, layers: int = 8) -> dict:
     feed-forward of 3 x width (the two matrices weigh what Zedotar's three of 2 x width do) or 2 of 16 experts."""
     heads = max(2, width // 128)
     kv = max(1, heads // 4)
-    par = dict(type="parallel", mixer=dict(left=dict(heads=heads, kv_heads=kv, dim=128, vdim=128, scale=128 ** -0.5, softcap=30.0),
-                                           right=dict(heads=width // 64, dim=64), left_scale=0.8, right_scale=0.9))
-    att = dict(type="attention", mixer=dict(heads=heads, kv_heads=kv, dim=64, vdim=128, scale=0.125, diff=0.3, mask=dict(size=1024)))
+    par = dict(type="parallel", mixer=dict(left=dict(heads=heads, kv_heads=kv, dim=128, vdim=128, scale=128 ** -0.5, softcap=50.0),
+                                           right=dict(heads=width // 64, dim=64), left_scale=1.0, right_scale=0.5))
+    att = dict(type="attention", mixer=dict(heads=heads, kv_heads=kv, dim=64, vdim=128, scale=0.125, diff=0.2, mask=dict(size=1024)))
     dense = dict(kind="dense", ff=3 * width)
-    moe = dict(kind="moe", router=dict(experts=16, top=2, scale=2.5), expert=dict(ff=width // 2))
+    moe = dict(kind="moe", router=dict(experts=16, top=2, scale=2.0), expert=dict(ff=width // 2))
     plan, first_att = [], None
     for i in range(layers):
         if i % 4 == 1:
@@ -720,7 +720,7 @@ def kernel_table_subivik(sm, zm, device, timer, T=4096):
         add(f"zedotar gemm dense gate|up + gelu [{n} x {W}] x [{gu.shape[0]} x {W}] ({tag})", ms,
             nbytes=gu.numel() * 2 + n * W * 2 + n * gu.shape[0], flops=2 * n * W * gu.shape[0])
         # residual + norm
-        ms = timer(lambda: Q.add_norm_dyt(x, pw["norm"], pw["norm_b"], 0.7, torch.bfloat16, delta=d, delta_mult=0.8, delta2=d2, delta2_mult=0.9))
+        ms = timer(lambda: Q.add_norm_dyt(x, pw["norm"], pw["norm_b"], 0.7, torch.bfloat16, delta=d, delta_mult=1.0, delta2=d2, delta2_mult=0.5))
         add(f"residual add of two mixers + tanh norm ({tag})", ms, nbytes=n * W * (4 + 4 + 4 + 4 + 2), like="residual add + rms norm")
         ms = timer(lambda: Q.add_rms_norm(x, d, mw["norm"], 1.0, zsp.norm_eps, torch.bfloat16))
         add(f"zedotar residual add + rms norm ({tag})", ms, nbytes=n * W * (4 + 4 + 4 + 2))
