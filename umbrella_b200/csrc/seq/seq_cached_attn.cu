@@ -314,37 +314,62 @@ __global__ void __launch_bounds__(32 * kCdWarps) cached_attention_decode_kernel(
     }
     const float hb = (MODE == UMBS_ATTN_SIGMOID && a.head_bias) ? a.head_bias[h] : 0.f;
     float m = -INFINITY, l = 0.f;
-    for (int k = lo + w; k < hi; k += kCdWarps) {
-        const T* src;
-        int dist = 0;
-        if (k < n_pool) src = (const T*)a.pool_cache + ((int64_t)slot * a.pool_len + k) * row_kv;
-        else {
-            const int j = j_lo + (k - n_pool);
-            dist = p - j;
-            src = j >= p ? (const T*)a.kv + (int64_t)t * row_kv : (const T*)a.kv_cache + ((int64_t)slot * a.kv_len + j % a.kv_len) * row_kv;
-        }
-        float dot = 0.f, vv[kCdMaxPerLane];
+    // Four of the warp's keys at a time: their key and value loads are all in flight before the first is needed; the
+    // softmax state then takes them one by one, in key order (the same additions as one key at a time).
+    constexpr int KU = 4;
+    for (int kb = lo + w; kb < hi; kb += kCdWarps * KU) {
+        const T* src[KU];
+        int dist[KU];
+        float dot[KU], vv[KU][kCdMaxPerLane];
 #pragma unroll
-        for (int i = 0; i < kCdMaxPerLane; ++i) {
-            const int d = lane + 32 * i;
-            if (d < dim) dot = fmaf(qv[i], to_f32(src[koff + d]), dot);
-            vv[i] = d < vdim ? to_f32(src[voff + d]) : 0.f;
-        }
-#pragma unroll
-        for (int x = 16; x > 0; x >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, x);
-        float pw;
-        if (MODE == UMBS_ATTN_SIGMOID) {
-            pw = sigmoidf_(dot * a.scale + hb);
-        } else {
-            const float sc = shaped_score(a, dot, r1h, r2h, dist), mn = fmaxf(m, sc), corr = expf(m - mn);   // m = -inf the first time: corr = 0
-            pw = expf(sc - mn);
-            l = l * corr + pw;
-            m = mn;
-#pragma unroll
-            for (int i = 0; i < kCdMaxPerLane; ++i) o[i] *= corr;
+        for (int u = 0; u < KU; ++u) {
+            const int k = min(kb + u * kCdWarps, hi - 1);           // (a place beyond the run reads the last key; unused)
+            dist[u] = 0;
+            if (k < n_pool) src[u] = (const T*)a.pool_cache + ((int64_t)slot * a.pool_len + k) * row_kv;
+            else {
+                const int j = j_lo + (k - n_pool);
+                dist[u] = p - j;
+                src[u] = j >= p ? (const T*)a.kv + (int64_t)t * row_kv
+                                : (const T*)a.kv_cache + ((int64_t)slot * a.kv_len + j % a.kv_len) * row_kv;
+            }
         }
 #pragma unroll
-        for (int i = 0; i < kCdMaxPerLane; ++i) o[i] = fmaf(pw, vv[i], o[i]);
+        for (int u = 0; u < KU; ++u) {
+            dot[u] = 0.f;
+#pragma unroll
+            for (int i = 0; i < kCdMaxPerLane; ++i) {
+                const int d = lane + 32 * i;
+                if (d < dim) dot[u] = fmaf(qv[i], to_f32(src[u][koff + d]), dot[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < KU; ++u)
+#pragma unroll
+            for (int i = 0; i < kCdMaxPerLane; ++i) {
+                const int d = lane + 32 * i;
+                vv[u][i] = d < vdim ? to_f32(src[u][voff + d]) : 0.f;
+            }
+#pragma unroll
+        for (int x = 16; x > 0; x >>= 1)
+#pragma unroll
+            for (int u = 0; u < KU; ++u) dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], x);
+#pragma unroll
+        for (int u = 0; u < KU; ++u) {
+            if (kb + u * kCdWarps >= hi) break;
+            float pw;
+            if (MODE == UMBS_ATTN_SIGMOID) {
+                pw = sigmoidf_(dot[u] * a.scale + hb);
+            } else {
+                const float sc = shaped_score(a, dot[u], r1h, r2h, dist[u]), mn = fmaxf(m, sc), corr = expf(m - mn);   // m = -inf the first time: corr = 0
+                pw = expf(sc - mn);
+                l = l * corr + pw;
+                m = mn;
+#pragma unroll
+                for (int i = 0; i < kCdMaxPerLane; ++i) o[i] *= corr;
+            }
+#pragma unroll
+            for (int i = 0; i < kCdMaxPerLane; ++i) o[i] = fmaf(pw, vv[u][i], o[i]);
+        }
     }
 #pragma unroll
     for (int i = 0; i < kCdMaxPerLane; ++i) sm_o[w][lane + 32 * i] = o[i];
